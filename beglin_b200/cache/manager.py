@@ -9,7 +9,8 @@ is read.
 
 Stages of the model whose mixers have equal needs form a group.  A group of paged keys and values
 has one pool of pages (shared by its stages: page p of every stage of the group belongs to the same
-request and the same positions) and one block table per request.  A group with a window gives back
+request and the same positions) and one block table per request.  What a page holds is the need's
+business (`page_shape`): keys and values per kv head, or one latent row per position.  A group with a window gives back
 the pages that lie wholly behind the window as a request advances.  A group of fixed state has one
 slab [stages, slots, ...]; a request's slot is zeroed when the request starts.
 
@@ -23,7 +24,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..parts.cache_need import FixedStateNeed, FixedStateView, PagedKVNeed, PagedKVView
+from ..parts.cache_need import PAGED_NEEDS, FixedStateNeed, FixedStateView, PagedKVNeed, PagedKVView
 
 
 class OutOfPages(RuntimeError):
@@ -75,11 +76,11 @@ class PagePool:
 
 
 class _KVGroup:
-    def __init__(self, need: PagedKVNeed, stages: List[int], num_pages: int):
+    def __init__(self, need, stages: List[int], num_pages: int):
         self.need, self.stages = need, stages
         self.pool = PagePool(num_pages)
         self.tables: Dict[Hashable, List[int]] = {}     # request -> page of each page index, -1 if none
-        self.device_pool: Optional[torch.Tensor] = None  # [stages, pages, 2, nkv, page, hd]
+        self.device_pool: Optional[torch.Tensor] = None  # [stages, pages, *need.page_shape]: [.., 2, nkv, page, hd] or [.., page, width]
 
     def first_needed_page(self, first_query_pos: int, page_size: int) -> int:
         if self.need.window is None:
@@ -110,7 +111,7 @@ class CacheManager:
         for stage, need in enumerate(needs):
             if need is None:
                 continue
-            if isinstance(need, PagedKVNeed):
+            if isinstance(need, PAGED_NEEDS):
                 groups, kind, make = self.kv_groups, "kv", lambda n: _KVGroup(n, [], num_pages)
             elif isinstance(need, FixedStateNeed):
                 groups, kind, make = self.state_groups, "state", lambda n: _StateGroup(n, [])
@@ -140,8 +141,8 @@ class CacheManager:
     # ---------------------------------------------------------------- device side
     def allocate(self, device, dtype: torch.dtype) -> None:
         for g in self.kv_groups:
-            g.device_pool = torch.empty((len(g.stages), self.num_pages + 1, 2, g.need.n_kv_heads, self.page_size,
-                                         g.need.head_dim), dtype=dtype, device=device)
+            g.device_pool = torch.empty((len(g.stages), self.num_pages + 1) + tuple(g.need.page_shape(self.page_size)),
+                                        dtype=dtype, device=device)
             g.device_pool[:, self.dump_page].zero_()
         for g in self.state_groups:
             g.slab = torch.zeros((len(g.stages), self.max_requests + 1) + tuple(g.need.shape),

@@ -115,6 +115,15 @@ class ConfigFields:
             raise ConfigError(f"{self.origin}: key '{key}' is not a number")
         return [v]
 
+    def mapping_list(self, key: str, required: bool = False) -> Optional[List["ConfigFields"]]:
+        """An array of objects (such as a list of layers), each as ConfigFields of its own."""
+        v, found = self._get(key, None, required)
+        if not found:
+            return None
+        if not isinstance(v, list) or not all(isinstance(m, dict) for m in v):
+            raise ConfigError(f"{self.origin}: key '{key}' is not an array of objects")
+        return [ConfigFields(m, f"{self.origin}:{key}[{i}]") for i, m in enumerate(v)]
+
     def mapping(self, key: str) -> Optional["ConfigFields"]:
         v, found = self._get(key, None, False)
         if not found:

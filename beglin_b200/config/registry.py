@@ -1,7 +1,7 @@
 """The one registry from an architecture's name to its configuration class and model spec.
 
-The name is `architectures[0]` of config.json; a folder without that key is resolved through
-`model_type` (the reference's C engine keys on `model_type` alone, qwen_infer.c:18989 and
+The name is `architectures[0]` of config.json, or the string `architecture`; a folder without
+either key is resolved through `model_type` (the reference's C engine keys on `model_type` alone, qwen_infer.c:18989 and
 :19360-19372, and its Python registry falls back to `architectures[0]`,
 tools/model_capability.py:793-815).  An unknown name is an error that lists the names known,
 in the manner of qwen_infer.c:19369.
@@ -38,10 +38,12 @@ def resolve_architecture(fields: ConfigFields) -> Architecture:
     name: Optional[str] = None
     if names:
         name = names[0]
+    elif fields.string("architecture") is not None:      # a folder that names its one architecture in a plain string
+        name = fields.string("architecture")
     elif model_type is not None:
         name = _MODEL_TYPES.get(model_type, model_type)
     if name is None:
-        raise ConfigError(f"{fields.origin} missing 'architectures' and 'model_type'")
+        raise ConfigError(f"{fields.origin} missing 'architectures', 'architecture' and 'model_type'")
     arch = ARCHITECTURES.get(name)
     if arch is None:
         known = ", ".join(sorted(ARCHITECTURES))

@@ -14,9 +14,12 @@ constexpr int GF_BM = 64, GF_BN = 64, GF_BK = 16, GF_THREADS = 256;
 __global__ void __launch_bounds__(GF_THREADS)
 gemm_f32_nt_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw,
                    const float* __restrict__ bias, float* __restrict__ C, int ldc,
-                   int M, int N, int K, int accumulate) {
+                   int M, int N, int K, int accumulate, long long batch_a, long long batch_w, long long batch_c) {
     pdl_launch();
     pdl_wait();
+    A += (size_t)blockIdx.z * batch_a;              // a batch of independent products: one per blockIdx.z
+    W += (size_t)blockIdx.z * batch_w;
+    C += (size_t)blockIdx.z * batch_c;
     __shared__ float As[GF_BK][GF_BM + 4];
     __shared__ float Ws[GF_BK][GF_BN + 4];
     const int tid = threadIdx.x;
@@ -77,7 +80,23 @@ extern "C" int bg_gemm_f32_nt(const float* A, int lda, const float* W, int ldw, 
     if (K <= 0) return BG_ERR_SHAPE;
     dim3 grid((N + bg::GF_BN - 1) / bg::GF_BN, (M + bg::GF_BM - 1) / bg::GF_BM);
     if (grid.y > 65535) return BG_ERR_SHAPE;
-    bg::launch(bg::gemm_f32_nt_kernel, grid, dim3(bg::GF_THREADS), 0, stream, A, lda, W, ldw, bias, C, ldc, M, N, K, accumulate);
+    bg::launch(bg::gemm_f32_nt_kernel, grid, dim3(bg::GF_THREADS), 0, stream, A, lda, W, ldw, bias, C, ldc, M, N, K, accumulate,
+               0LL, 0LL, 0LL);
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+// `batch` products of the same shape: product b reads A + b * batch_a and W + b * batch_w and writes C + b * batch_c
+// (element counts).  No bias.  The per-head products of an attention that works in a latent space are of this kind.
+extern "C" int bg_gemm_f32_nt_batched(const float* A, int lda, long long batch_a, const float* W, int ldw, long long batch_w,
+                                      float* C, int ldc, long long batch_c, int batch, int M, int N, int K,
+                                      cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return BG_OK;
+    if (K <= 0 || batch > 65535) return BG_ERR_SHAPE;
+    dim3 grid((N + bg::GF_BN - 1) / bg::GF_BN, (M + bg::GF_BM - 1) / bg::GF_BM, batch);
+    if (grid.y > 65535) return BG_ERR_SHAPE;
+    bg::launch(bg::gemm_f32_nt_kernel, grid, dim3(bg::GF_THREADS), 0, stream, A, lda, W, ldw, (const float*)nullptr, C, ldc, M, N,
+               K, 0, batch_a, batch_w, batch_c);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

@@ -1,0 +1,342 @@
+// Attention through a low-rank latent, over a paged cache that holds, per position, ONE row for all
+// heads: the normed latent c [rank] followed by the rotated key part k_r [rot] that the heads share.
+//
+// The per-head keys W_uk c and values W_uv c are never made.  With a = W_uk^T q_plain (the query
+// carried into the latent space, a product that the caller runs per head), the score of a key is
+//   s_t = (a . c_t + q_rot . k_r,t) * scale,
+// and with the softmax weights p the head's result in the latent space is o = sum_t p_t c_t, from which
+// the caller makes W_uv o.  So every head attends over the same cached rows: the first `rank` features
+// of a row serve as its value.
+//
+// The layout of the work is that of the grouped-query kernel (attention.cu): query blocks of up to `bq`
+// consecutive rows of one request, keys cut into splits at absolute positions, one CTA per (query block,
+// chunk of heads, split) that streams its keys once for all its rows and writes, per (row, head), a
+// running maximum, a running sum and an unnormalised result; a merge kernel joins the splits in order.
+// Everything is float, and a row shares no accumulator with another row, so a row's result does not
+// depend on how the step was cut or on what else is in the batch.
+#include "common.cuh"
+
+namespace bg {
+
+constexpr int LAT_THREADS = 256;
+constexpr int LAT_WARPS = LAT_THREADS / 32;
+
+// One row per step row: the RMS norm of the latent and the rotation of the shared key part, stored at the
+// row's position in the pages.  src row = [.. | latent raw (rank) | key part raw (rot) | ..] from col0.
+// Pairs (2i, 2i+1) of the first rot_dims features of the key part turn by the row's angles; the rest pass.
+template <typename TI, typename TW, typename TC>
+__global__ void latent_append_kernel(const TI* __restrict__ src, int src_stride, int col0, int rank, int rot, int rot_dims,
+                                     const TW* __restrict__ w, float eps, const float* __restrict__ cos_sin,
+                                     const int* __restrict__ positions, const int* __restrict__ row_req,
+                                     const int* __restrict__ block_table, int max_pages, TC* __restrict__ pool,
+                                     int num_pages, int page_size, unsigned* status) {
+    __shared__ float red[32];
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const TI* s = src + (size_t)t * src_stride + col0;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+        const float v = to_float(s[i]);
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
+    const int pos = positions[t];
+    const int page = block_table[(size_t)row_req[t] * max_pages + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0 && status) atomicOr(status, BG_STATUS_BAD_PAGE);
+        return;
+    }
+    const int width = rank + rot;
+    TC* dst = pool + ((size_t)page * page_size + pos % page_size) * width;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_float<TC>(to_float(s[i]) * inv * to_float(w[i]));
+    const int half = rot_dims / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float u = to_float(s[rank + 2 * i]), v = to_float(s[rank + 2 * i + 1]);
+        const float c = cos_sin[((size_t)t * half + i) * 2], sn = cos_sin[((size_t)t * half + i) * 2 + 1];
+        dst[rank + 2 * i] = from_float<TC>(u * c - v * sn);
+        dst[rank + 2 * i + 1] = from_float<TC>(v * c + u * sn);
+    }
+    for (int i = rot_dims + threadIdx.x; i < rot; i += blockDim.x) dst[rank + i] = from_float<TC>(to_float(s[rank + i]));
+}
+
+struct LatentParams {
+    const void* q_lat;      // [H][T][rank] queries in the latent space: element (h, t, i) at h*ql_head + t*ql_row + i
+    long long ql_head;
+    int ql_row;
+    const void* q_raw;      // [T][H][dim + rot] the query product's rows: the rot part of head h starts at h*(dim+rot) + dim
+    int qr_row, qr_head, qr_off;
+    const float* cos_sin;   // [T][rot_dims/2][2]
+    const void* pool;       // [num_pages][page_size][rank + rot]
+    int num_pages, page_size;
+    const int* block_table; // [B, max_pages]
+    int max_pages;
+    const int* positions;   // [T]
+    const int* qblk;        // [n_qblk][3] = (request, first row, number of rows)
+    float* part_o;          // [T*H][max_splits][rank]
+    float* part_ml;         // [T*H][max_splits][2]
+    int max_splits;
+    int H, hc;              // heads, heads per CTA
+    int rank, rot, rot_dims;
+    int split, tile, bq;
+    float scale;
+    unsigned* status;
+};
+
+template <typename TQ, typename TR, typename TC>
+__global__ void __launch_bounds__(LAT_THREADS)
+latent_attention_partial_kernel(LatentParams p) {
+    extern __shared__ float smem[];
+    const int rank = p.rank, width = p.rank + p.rot;
+    const int kstride = width + 1;
+    const int rows_max = p.bq * p.hc;
+    float* q_s = smem;                                       // [rows_max][width]
+    float* acc_s = q_s + (size_t)rows_max * width;           // [rows_max][rank]
+    float* k_s = acc_s + (size_t)rows_max * rank;            // [tile][width + 1]
+    float* p_s = k_s + (size_t)p.tile * kstride;             // [warps][tile]
+    float* m_s = p_s + LAT_WARPS * p.tile;                   // [rows_max]
+    float* l_s = m_s + rows_max;                             // [rows_max]
+    long long* base_s = (long long*)(l_s + rows_max + ((rows_max * (width + rank + 2) + p.tile * (kstride + LAT_WARPS)) & 1));
+
+    pdl_launch();
+    pdl_wait();
+    const int qb = blockIdx.x, hchunk = blockIdx.y, sp = blockIdx.z;
+    const int req = p.qblk[qb * 3 + 0], row0 = p.qblk[qb * 3 + 1], nq = p.qblk[qb * 3 + 2];
+    if (nq <= 0) return;
+    const int h0 = hchunk * p.hc;
+    const int nh = min(p.hc, p.H - h0);
+    const int pos_last = p.positions[row0 + nq - 1];
+    const int k_begin = sp * p.split;
+    const int k_end = min((sp + 1) * p.split, pos_last + 1);       // exclusive
+    if (k_begin >= k_end) return;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_rows = nq * nh;                                    // row r = (query qi, head h0 + g), r = qi * nh + g
+    const TQ* ql = (const TQ*)p.q_lat;
+    const TR* qr = (const TR*)p.q_raw;
+    const int half = p.rot_dims / 2;
+    for (int idx = tid; idx < n_rows * width; idx += LAT_THREADS) {
+        const int r = idx / width, d = idx - r * width;
+        const int qi = r / nh, g = r - qi * nh;
+        const int t = row0 + qi, h = h0 + g;
+        float v;
+        if (d < rank) {
+            v = to_float(ql[(size_t)h * p.ql_head + (size_t)t * p.ql_row + d]);
+        } else {
+            const int e = d - rank;
+            const TR* src = qr + (size_t)t * p.qr_row + (size_t)h * p.qr_head + p.qr_off;
+            if (e < p.rot_dims) {
+                const int i = e >> 1;
+                const float u = to_float(src[2 * i]), w = to_float(src[2 * i + 1]);
+                const float c = p.cos_sin[((size_t)t * half + i) * 2], sn = p.cos_sin[((size_t)t * half + i) * 2 + 1];
+                v = (e & 1) ? (w * c + u * sn) : (u * c - w * sn);
+            } else {
+                v = to_float(src[e]);
+            }
+        }
+        q_s[idx] = v;
+    }
+    for (int idx = tid; idx < n_rows * rank; idx += LAT_THREADS) acc_s[idx] = 0.0f;
+    for (int r = tid; r < n_rows; r += LAT_THREADS) { m_s[r] = -INFINITY; l_s[r] = 0.0f; }
+
+    const TC* pool = (const TC*)p.pool;
+    const int tile = p.tile;
+    float* pw = p_s + warp * tile;
+
+    for (int t0 = k_begin; t0 < k_end; t0 += tile) {               // k_begin is a multiple of split, split of tile
+        __syncthreads();
+        for (int j = tid; j < tile; j += LAT_THREADS) {
+            const int key = t0 + j;
+            long long off = -1;
+            if (key < k_end) {
+                const int page = p.block_table[(size_t)req * p.max_pages + key / p.page_size];
+                if (page < 0 || page >= p.num_pages) {
+                    if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE);
+                } else {
+                    off = (long long)(((size_t)page * p.page_size + key % p.page_size) * width);
+                }
+            }
+            base_s[j] = off;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < tile * width; idx += LAT_THREADS) {
+            const int j = idx / width, d = idx - j * width;
+            const long long off = base_s[j];
+            k_s[j * kstride + d] = off >= 0 ? to_float(pool[off + d]) : 0.0f;
+        }
+        __syncthreads();
+
+        for (int r = warp; r < n_rows; r += LAT_WARPS) {
+            const int qi = r / nh;
+            const int pos = p.positions[row0 + qi];
+            const float* qrow = q_s + (size_t)r * width;
+            float s[2];
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                s[c] = -INFINITY;
+                const int j = c * 32 + lane;
+                if (j < tile) {
+                    const int key = t0 + j;
+                    if (key <= pos && key < k_end && base_s[j] >= 0) {
+                        const float* kr = k_s + j * kstride;
+                        float dot = 0.0f;
+                        for (int d = 0; d < width; ++d) dot = fmaf(qrow[d], kr[d], dot);
+                        s[c] = dot * p.scale;
+                    }
+                }
+                tmax = fmaxf(tmax, s[c]);
+            }
+            tmax = warp_max(tmax);
+            if (tmax == -INFINITY) continue;                       // no visible key of this tile for this row
+            const float m_old = m_s[r];
+            const float m_new = fmaxf(m_old, tmax);
+            const float corr = (m_old == -INFINITY) ? 0.0f : expf(m_old - m_new);
+            float psum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                s[c] = (s[c] == -INFINITY) ? 0.0f : expf(s[c] - m_new);
+                psum += s[c];
+                if (c * 32 + lane < tile) pw[c * 32 + lane] = s[c];
+            }
+            psum = warp_sum(psum);
+            __syncwarp();
+            float* ar = acc_s + (size_t)r * rank;
+            for (int d = lane; d < rank; d += 32) {
+                float a = ar[d] * corr;
+                for (int jj = 0; jj < tile; ++jj) a = fmaf(pw[jj], k_s[jj * kstride + d], a);
+                ar[d] = a;
+            }
+            if (lane == 0) { m_s[r] = m_new; l_s[r] = l_s[r] * corr + psum; }
+            __syncwarp();
+        }
+    }
+    __syncthreads();
+    // partial results, only for rows that see at least one key of this split
+    for (int r = warp; r < n_rows; r += LAT_WARPS) {
+        const int qi = r / nh, g = r - qi * nh;
+        const int pos = p.positions[row0 + qi];
+        if (pos < k_begin) continue;
+        const size_t prow = ((size_t)(row0 + qi) * p.H + h0 + g) * p.max_splits + sp;
+        for (int d = lane; d < rank; d += 32) p.part_o[prow * rank + d] = acc_s[(size_t)r * rank + d];
+        if (lane == 0) { p.part_ml[prow * 2 + 0] = m_s[r]; p.part_ml[prow * 2 + 1] = l_s[r]; }
+    }
+}
+
+// out[h][t][:] = sum_s o_s e^(m_s - m) / sum_s l_s e^(m_s - m) over the splits 0 .. position / split, in split
+// order.  One warp per (row, head).
+template <typename TO>
+__global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              const int* __restrict__ positions, TO* __restrict__ out, long long out_head,
+                                              int out_row, int T, int H, int rank, int max_splits, int split) {
+    pdl_launch();
+    pdl_wait();
+    const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= T * H) return;
+    const int t = w / H, h = w - t * H;
+    const int s_hi = positions[t] / split;
+    const size_t prow = (size_t)w * max_splits;
+    float m = -INFINITY;
+    for (int s = lane; s <= s_hi; s += 32) m = fmaxf(m, part_ml[(prow + s) * 2]);
+    m = warp_max(m);
+    float l = 0.0f;
+    for (int s = 0; s <= s_hi; ++s) l = fmaf(part_ml[(prow + s) * 2 + 1], expf(part_ml[(prow + s) * 2] - m), l);
+    const float inv = 1.0f / l;
+    TO* o = out + (size_t)h * out_head + (size_t)t * out_row;
+    for (int d = lane; d < rank; d += 32) {
+        float acc = 0.0f;
+        for (int s = 0; s <= s_hi; ++s) acc = fmaf(part_o[(prow + s) * rank + d], expf(part_ml[(prow + s) * 2] - m), acc);
+        o[d] = from_float<TO>(acc * inv);
+    }
+}
+
+}  // namespace bg
+
+using namespace bg;
+
+static size_t latent_smem_bytes(int rows, int rank, int rot, int tile) {
+    const size_t width = (size_t)rank + rot;
+    size_t floats = (size_t)rows * (width + rank + 2) + (size_t)tile * (width + 1 + LAT_WARPS);
+    floats += floats & 1;
+    return floats * sizeof(float) + (size_t)tile * sizeof(long long);
+}
+
+// Rows per CTA (queries x heads) and keys per tile that fit one CTA's shared memory for these sizes.
+extern "C" int bg_latent_attention_plan(int rank, int rot, int* rows_out, int* tile_out) {
+    if (rank <= 0 || rot < 0) return BG_ERR_UNSUPPORTED;
+    const size_t limit = 200 * 1024;
+    for (int rows = 64; rows >= 1; rows >>= 1) {
+        for (int tile = 64; tile >= 32; tile >>= 1) {
+            if (latent_smem_bytes(rows, rank, rot, tile) <= limit) { *rows_out = rows; *tile_out = tile; return BG_OK; }
+        }
+    }
+    return BG_ERR_UNSUPPORTED;
+}
+
+extern "C" int bg_latent_append(const void* src, int src_dtype, int src_stride, int col0, int rank, int rot, int rot_dims,
+                                const void* w, int w_dtype, float eps, const float* cos_sin, const int* positions,
+                                const int* row_req, const int* block_table, int max_pages, void* pool, int pool_dtype,
+                                int num_pages, int page_size, int n_rows, unsigned* status, cudaStream_t stream) {
+    if (n_rows <= 0) return BG_OK;
+    if (rank <= 0 || rot < 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1)) return BG_ERR_SHAPE;
+    BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(w_dtype, TW, BG_DISPATCH_DTYPE(pool_dtype, TC,
+        launch(latent_append_kernel<TI, TW, TC>, dim3(n_rows), dim3(128), 0, stream, (const TI*)src, src_stride, col0, rank,
+               rot, rot_dims, (const TW*)w, eps, cos_sin, positions, row_req, block_table, max_pages, (TC*)pool, num_pages,
+               page_size, status))));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_latent_attention_partial(const void* q_lat, int ql_dtype, long long ql_head, int ql_row, const void* q_raw,
+                                           int qr_dtype, int qr_row, int qr_head, int qr_off, const float* cos_sin,
+                                           const void* pool, int pool_dtype, int num_pages, int page_size,
+                                           const int* block_table, int max_pages, const int* positions, const int* qblk,
+                                           int n_qblk, float* part_o, float* part_ml, int max_splits, int n_splits_launch,
+                                           int H, int hc, int rank, int rot, int rot_dims, int split, int tile, int bq,
+                                           float scale, unsigned* status, cudaStream_t stream) {
+    if (n_qblk <= 0 || n_splits_launch <= 0) return BG_OK;
+    if (H <= 0 || hc <= 0 || hc > H || rank <= 0 || rot < 0 || rot_dims > rot || (rot_dims & 1)) return BG_ERR_SHAPE;
+    if ((tile != 32 && tile != 64) || split % tile != 0 || bq <= 0) return BG_ERR_SHAPE;
+    const int chunks = (H + hc - 1) / hc;
+    if (n_splits_launch > max_splits || n_splits_launch > 65535 || chunks > 65535) return BG_ERR_SHAPE;
+    LatentParams p;
+    p.q_lat = q_lat; p.ql_head = ql_head; p.ql_row = ql_row; p.q_raw = q_raw; p.qr_row = qr_row; p.qr_head = qr_head;
+    p.qr_off = qr_off; p.cos_sin = cos_sin; p.pool = pool; p.num_pages = num_pages; p.page_size = page_size;
+    p.block_table = block_table; p.max_pages = max_pages; p.positions = positions; p.qblk = qblk; p.part_o = part_o;
+    p.part_ml = part_ml; p.max_splits = max_splits; p.H = H; p.hc = hc; p.rank = rank; p.rot = rot; p.rot_dims = rot_dims;
+    p.split = split; p.tile = tile; p.bq = bq; p.scale = scale; p.status = status;
+    const size_t smem = latent_smem_bytes(bq * hc, rank, rot, tile);
+    if (smem > 227 * 1024) return BG_ERR_UNSUPPORTED;
+    dim3 grid(n_qblk, chunks, n_splits_launch);
+#define BG_LAT_LAUNCH(TQ, TR, TC)                                                                          \
+    do {                                                                                                   \
+        auto kern = latent_attention_partial_kernel<TQ, TR, TC>;                                           \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return (int)e;                                                               \
+        launch(kern, grid, dim3(LAT_THREADS), smem, stream, p);                                            \
+    } while (0)
+    if (ql_dtype != BG_DTYPE_F32) return BG_ERR_DTYPE;             // the queries in the latent space come as float
+    if (qr_dtype == BG_DTYPE_F32 && pool_dtype == BG_DTYPE_F32) BG_LAT_LAUNCH(float, float, float);
+    else if (qr_dtype == BG_DTYPE_BF16 && pool_dtype == BG_DTYPE_BF16) BG_LAT_LAUNCH(float, __nv_bfloat16, __nv_bfloat16);
+    else if (qr_dtype == BG_DTYPE_F32 && pool_dtype == BG_DTYPE_BF16) BG_LAT_LAUNCH(float, float, __nv_bfloat16);
+    else if (qr_dtype == BG_DTYPE_BF16 && pool_dtype == BG_DTYPE_F32) BG_LAT_LAUNCH(float, __nv_bfloat16, float);
+    else return BG_ERR_DTYPE;
+#undef BG_LAT_LAUNCH
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_latent_attention_merge(const float* part_o, const float* part_ml, const int* positions, void* out,
+                                         int out_dtype, long long out_head, int out_row, int T, int H, int rank,
+                                         int max_splits, int split, cudaStream_t stream) {
+    const long long warps = (long long)T * H;
+    if (warps <= 0) return BG_OK;
+    const unsigned blocks = (unsigned)((warps + 7) / 8);
+    BG_DISPATCH_DTYPE(out_dtype, TO,
+        launch(latent_attention_merge_kernel<TO>, dim3(blocks), dim3(256), 0, stream, part_o, part_ml, positions, (TO*)out,
+               out_head, out_row, T, H, rank, max_splits, split));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}

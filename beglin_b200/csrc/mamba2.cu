@@ -1,0 +1,273 @@
+// The Mamba-2 recurrence for a ragged step: every request brings a run of consecutive tokens (a prompt
+// portion or one decoded token) and owns one slot of fixed state, float32:
+//   slot = [ S: heads x N x P | conv: (taps - 1) x channels ]
+// S is the state of the recurrence, conv the last taps-1 inputs of the causal convolution (oldest first).
+// A slot is zero when its request starts, so a convolution that reaches back beyond a sequence's first
+// token finds zeros there.  Four kernels: the convolution with SiLU, the update of its state, the scan, and the gate
+// with the grouped RMS norm.  Everything that enters the recurrence is float: step sizes, decays, B, C, x.
+//
+// Requests are given as a list of (request, first row, number of rows), one entry per request of the step.
+#include "common.cuh"
+
+namespace bg {
+
+__device__ __forceinline__ float softplus32(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float silu32(float z) { return z / (1.0f + expf(-z)); }
+
+// out[t, c] = silu(b[c] + sum_j w[c, j] * in(t - (taps-1-j), c)), in(.) taken from the step's rows of the same
+// request or, further back, from the slot's conv state.  src row = [.. | channels from col0 | ..].
+template <typename TI, typename TW>
+__global__ void conv_silu_kernel(const TI* __restrict__ src, int src_stride, int col0, int channels, int taps,
+                                 const TW* __restrict__ w, const TW* __restrict__ b, const float* __restrict__ state,
+                                 size_t slot_stride, size_t conv_off, const int* __restrict__ slots,
+                                 const int* __restrict__ row_req, const int* __restrict__ reqs, float* __restrict__ out) {
+    pdl_launch();
+    pdl_wait();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int t = blockIdx.x;
+    if (c >= channels) return;
+    const int req = row_req[t];
+    const int row0 = reqs[req * 3 + 1];
+    const int j = t - row0;                                   // rows of this request before this one in the step
+    const float* st = state + (size_t)slots[req] * slot_stride + conv_off;
+    float acc = to_float(b[c]);
+    for (int k = 0; k < taps; ++k) {
+        const int back = taps - 1 - k;
+        float v;
+        if (back <= j) v = to_float(src[(size_t)(t - back) * src_stride + col0 + c]);
+        else v = st[(size_t)(taps - 1 - (back - j)) * channels + c];
+        acc = fmaf(to_float(w[(size_t)c * taps + k]), v, acc);
+    }
+    out[(size_t)t * channels + c] = silu32(acc);
+}
+
+// The slot's conv state after the step: the last taps-1 inputs of (old state, the step's n rows).
+template <typename TI>
+__global__ void conv_state_kernel(const TI* __restrict__ src, int src_stride, int col0, int channels, int taps,
+                                  float* __restrict__ state, size_t slot_stride, size_t conv_off,
+                                  const int* __restrict__ slots, const int* __restrict__ reqs) {
+    pdl_launch();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int req = blockIdx.y;
+    if (c >= channels) return;
+    const int row0 = reqs[req * 3 + 1], n = reqs[req * 3 + 2];
+    if (n <= 0) return;
+    float* st = state + (size_t)slots[req] * slot_stride + conv_off;
+    const int keep = taps - 1;
+    for (int k = 0; k < keep; ++k) {                          // reads run ahead of writes: k + n > k
+        const int idx = k + n;                                // index into (old state ++ new rows)
+        const float v = idx < keep ? st[(size_t)idx * channels + c]
+                                   : to_float(src[(size_t)(row0 + idx - keep) * src_stride + col0 + c]);
+        st[(size_t)k * channels + c] = v;
+    }
+}
+
+// The scan.  One CTA per (head, request); thread (p, ns) = tid / NS, tid % NS owns S[n][p] for n = ns, ns + NS, ...
+// (NPT of them, in registers).  Per token:
+//   dt = softplus(dt_raw + dt_bias);  S = e^(-e^(A_log) dt) S + dt B x^T;  y = S^T C + D x.
+// The tokens go through shared memory in chunks of SCAN_CHUNK; the sum over n ends with shuffles among the NS
+// neighbouring lanes of a p.  A token's arithmetic does not depend on where the step was cut.
+constexpr int SCAN_CHUNK = 16;
+
+template <typename TI, typename TW, int NPT>
+__global__ void ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restrict__ src, int src_stride,
+                                int dt_col, const TW* __restrict__ dt_bias, const TW* __restrict__ A_log,
+                                const TW* __restrict__ Dw, float* __restrict__ state, size_t slot_stride,
+                                const int* __restrict__ slots, const int* __restrict__ reqs, float* __restrict__ y,
+                                int H, int P, int N, int G, int NS) {
+    extern __shared__ float sm[];
+    float* B_s = sm;                              // [CHUNK][N]
+    float* C_s = B_s + SCAN_CHUNK * N;            // [CHUNK][N]
+    float* x_s = C_s + SCAN_CHUNK * N;            // [CHUNK][P]
+    float* y_s = x_s + SCAN_CHUNK * P;            // [CHUNK][P]
+    float* dt_s = y_s + SCAN_CHUNK * P;           // [CHUNK]
+    float* da_s = dt_s + SCAN_CHUNK;              // [CHUNK]
+    pdl_launch();
+    pdl_wait();
+    const int h = blockIdx.x, req = blockIdx.y;
+    const int row0 = reqs[req * 3 + 1], n = reqs[req * 3 + 2];
+    if (n <= 0) return;
+    const int tid = threadIdx.x;
+    const int pcol = tid / NS, ns = tid - pcol * NS;
+    const bool live = pcol < P;
+    const int g = h / (H / G);
+    const int inner = H * P;
+    float* st = state + (size_t)slots[req] * slot_stride + (size_t)h * N * P;
+    float S[NPT];
+#pragma unroll
+    for (int k = 0; k < NPT; ++k) {
+        const int nn = ns + k * NS;
+        S[k] = (live && nn < N) ? st[(size_t)nn * P + pcol] : 0.0f;
+    }
+    const float a = expf(to_float(A_log[h]));
+    const float bias = to_float(dt_bias[h]);
+    const float Dh = to_float(Dw[h]);
+    const float* Bsrc = xbc + inner + (size_t)g * N;
+    const float* Csrc = xbc + inner + (size_t)G * N + (size_t)g * N;
+    for (int c0 = 0; c0 < n; c0 += SCAN_CHUNK) {
+        const int tc = min(SCAN_CHUNK, n - c0);
+        __syncthreads();
+        for (int idx = tid; idx < tc * N; idx += blockDim.x) {
+            const int tt = idx / N, nn = idx - tt * N;
+            const size_t row = (size_t)(row0 + c0 + tt) * channels;
+            B_s[tt * N + nn] = Bsrc[row + nn];
+            C_s[tt * N + nn] = Csrc[row + nn];
+        }
+        for (int idx = tid; idx < tc * P; idx += blockDim.x) {
+            const int tt = idx / P, pp = idx - tt * P;
+            x_s[tt * P + pp] = xbc[(size_t)(row0 + c0 + tt) * channels + (size_t)h * P + pp];
+        }
+        if (tid < tc) {
+            const float dt = softplus32(to_float(src[(size_t)(row0 + c0 + tid) * src_stride + dt_col + h]) + bias);
+            dt_s[tid] = dt;
+            da_s[tid] = expf(-a * dt);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < tc; ++tt) {
+            const float dt = dt_s[tt], dA = da_s[tt];
+            const float xv = live ? x_s[tt * P + pcol] : 0.0f;
+            const float dtx = dt * xv;
+            const float* Bt = B_s + tt * N;
+            const float* Ct = C_s + tt * N;
+            float yv = 0.0f;
+#pragma unroll
+            for (int k = 0; k < NPT; ++k) {
+                const int nn = ns + k * NS;
+                if (nn < N) {
+                    S[k] = fmaf(dA, S[k], dtx * Bt[nn]);
+                    yv = fmaf(S[k], Ct[nn], yv);
+                }
+            }
+            for (int off = NS >> 1; off > 0; off >>= 1) yv += __shfl_xor_sync(0xffffffffu, yv, off);
+            if (live && ns == 0) y_s[tt * P + pcol] = fmaf(Dh, xv, yv);
+        }
+        __syncthreads();
+        for (int idx = tid; idx < tc * P; idx += blockDim.x) {
+            const int tt = idx / P, pp = idx - tt * P;
+            y[(size_t)(row0 + c0 + tt) * inner + (size_t)h * P + pp] = y_s[tt * P + pp];
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < NPT; ++k) {
+        const int nn = ns + k * NS;
+        if (live && nn < N) st[(size_t)nn * P + pcol] = S[k];
+    }
+}
+
+// out[t, i] = v * rsqrt(mean over i's group of v^2 + eps) * w[i],  v = y[t, i] * silu(z[t, i]); the row is cut
+// into `groups` equal parts, each with a root mean square of its own.  z = src[t, z_col + i].  One block per
+// (row, group).
+template <typename TI, typename TW, typename TO>
+__global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const TI* __restrict__ src, int src_stride, int z_col,
+                                           const TW* __restrict__ w, float eps, TO* __restrict__ out, int inner, int groups) {
+    extern __shared__ float row_buf[];
+    __shared__ float red[32];
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x, g = blockIdx.y;
+    const int gs = inner / groups;
+    const int i0 = g * gs;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        const float z = to_float(src[(size_t)t * src_stride + z_col + i0 + i]);
+        const float v = y[(size_t)t * inner + i0 + i] * silu32(z);
+        row_buf[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)gs + eps);
+    for (int i = threadIdx.x; i < gs; i += blockDim.x)
+        out[(size_t)t * inner + i0 + i] = from_float<TO>(row_buf[i] * inv * to_float(w[i0 + i]));
+}
+
+}  // namespace bg
+
+using namespace bg;
+
+extern "C" int bg_conv_silu(const void* src, int src_dtype, int src_stride, int col0, int channels, int taps, const void* w,
+                            const void* b, int w_dtype, float* state, long long slot_stride, long long conv_off,
+                            const int* slots, const int* row_req, const int* reqs, int n_req, float* out, int n_rows,
+                            cudaStream_t stream) {
+    if (n_rows <= 0 || n_req <= 0) return BG_OK;
+    if (channels <= 0 || taps < 1 || n_req > 65535) return BG_ERR_SHAPE;
+    const unsigned bx = (unsigned)((channels + 127) / 128);
+    if (bx > 65535) return BG_ERR_SHAPE;
+    BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(w_dtype, TW,
+        launch(conv_silu_kernel<TI, TW>, dim3(n_rows, bx), dim3(128), 0, stream, (const TI*)src, src_stride, col0, channels,
+               taps, (const TW*)w, (const TW*)b, (const float*)state, (size_t)slot_stride, (size_t)conv_off, slots, row_req,
+               reqs, out)));
+    BG_LAUNCH_CHECK();
+    if (taps > 1) {
+        BG_DISPATCH_DTYPE(src_dtype, TI,
+            launch(conv_state_kernel<TI>, dim3(bx, n_req), dim3(128), 0, stream, (const TI*)src, src_stride, col0, channels,
+                   taps, state, (size_t)slot_stride, (size_t)conv_off, slots, reqs));
+        BG_LAUNCH_CHECK();
+    }
+    return BG_OK;
+}
+
+// How the scan lays a head's state over a CTA: NS lanes share a column p (a power of two up to 32, with
+// P * NS threads at most 1024), each holding ceil(N / NS) values.  Returns 0, or BG_ERR_UNSUPPORTED.
+static int scan_layout(int P, int N, int* ns_out, int* npt_out) {
+    if (P <= 0 || N <= 0 || P > 1024) return BG_ERR_UNSUPPORTED;
+    int ns = 1;
+    while (ns < 32 && P * ns * 2 <= 512 && ns * 2 <= N) ns *= 2;
+    while (ns < 32 && (N + ns - 1) / ns > 64 && P * ns * 2 <= 1024) ns *= 2;
+    const int npt = (N + ns - 1) / ns;
+    if (npt > 64) return BG_ERR_UNSUPPORTED;
+    *ns_out = ns; *npt_out = npt;
+    return BG_OK;
+}
+
+extern "C" int bg_ssm_scan(const float* xbc, int channels, const void* src, int src_dtype, int src_stride, int dt_col,
+                           const void* dt_bias, const void* A_log, const void* D, int w_dtype, float* state,
+                           long long slot_stride, const int* slots, const int* reqs, int n_req, float* y, int H, int P,
+                           int N, int G, cudaStream_t stream) {
+    if (n_req <= 0) return BG_OK;
+    if (H <= 0 || G <= 0 || H % G != 0 || n_req > 65535) return BG_ERR_SHAPE;
+    int ns = 0, npt = 0;
+    if (scan_layout(P, N, &ns, &npt) != BG_OK) return BG_ERR_UNSUPPORTED;
+    const int threads = (P * ns + 31) / 32 * 32;
+    const size_t smem = (size_t)(SCAN_CHUNK * (2 * N + 2 * P + 2)) * sizeof(float);
+    if (smem > 200 * 1024) return BG_ERR_UNSUPPORTED;
+    dim3 grid(H, n_req);
+#define BG_SCAN(NPT)                                                                                                  \
+    do {                                                                                                              \
+        auto kern = ssm_scan_kernel<TI, TW, NPT>;                                                                     \
+        if (smem > BG_SMEM_OPT_IN) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch(kern, grid, dim3(threads), smem, stream, xbc, channels, (const TI*)src, src_stride, dt_col,            \
+               (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, state, (size_t)slot_stride, slots, reqs, y, H, P, N, G, ns); \
+    } while (0)
+    BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(w_dtype, TW, {
+        if (npt <= 1) BG_SCAN(1);
+        else if (npt <= 2) BG_SCAN(2);
+        else if (npt <= 4) BG_SCAN(4);
+        else if (npt <= 8) BG_SCAN(8);
+        else if (npt <= 16) BG_SCAN(16);
+        else if (npt <= 32) BG_SCAN(32);
+        else BG_SCAN(64);
+    }));
+#undef BG_SCAN
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_gated_group_rmsnorm(const float* y, const void* src, int src_dtype, int src_stride, int z_col, const void* w,
+                                      int w_dtype, float eps, void* out, int out_dtype, int n_rows, int inner, int groups,
+                                      cudaStream_t stream) {
+    if (n_rows <= 0) return BG_OK;
+    if (groups <= 0 || inner % groups != 0 || groups > 65535) return BG_ERR_SHAPE;
+    const int gs = inner / groups;
+    const size_t smem = (size_t)gs * sizeof(float);
+    if (smem > 200 * 1024) return BG_ERR_SHAPE;
+    const int threads = gs >= 256 ? 256 : (gs + 31) / 32 * 32;
+    BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(w_dtype, TW, BG_DISPATCH_DTYPE(out_dtype, TO, {
+        auto kern = gated_group_rmsnorm_kernel<TI, TW, TO>;
+        if (smem > BG_SMEM_OPT_IN) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch(kern, dim3(n_rows, groups), dim3(threads), smem, stream, y, (const TI*)src, src_stride, z_col, (const TW*)w, eps,
+               (TO*)out, inner, groups);
+    })));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}

@@ -57,6 +57,32 @@ _SIGNATURES = {
                            _c_void_p, _c_float, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                            _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                            _c_void_p],
+    "bg_add_layernorm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_float, _c_void_p, _c_int,
+                         _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_depth_mix": [_c_void_p, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_ll, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p],
+    "bg_xielu": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_void_p, _c_int, _c_ll, _c_void_p],
+    "bg_rmsnorm_slice": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_int,
+                         _c_int, _c_void_p],
+    "bg_gate_heads": [_c_void_p, _c_int, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int,
+                      _c_int, _c_void_p],
+    "bg_latent_attention_plan": [_c_int, _c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
+    "bg_latent_append": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_float, _c_void_p,
+                         _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                         _c_void_p],
+    "bg_latent_attention_partial": [_c_void_p, _c_int, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                                    _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
+                                    _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                    _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+    "bg_latent_attention_merge": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int,
+                                  _c_int, _c_int, _c_void_p],
+    "bg_conv_silu": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_ll,
+                     _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p],
+    "bg_ssm_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                    _c_ll, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_gated_group_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_float, _c_void_p, _c_int,
+                               _c_int, _c_int, _c_int, _c_void_p],
+    "bg_gemm_f32_nt_batched": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_int, _c_ll, _c_void_p, _c_int, _c_ll, _c_int, _c_int,
+                               _c_int, _c_int, _c_void_p],
     "bg_sample": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "bg_sample_feed": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                        _c_void_p],
@@ -781,3 +807,241 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: O
                                     _p(feed_positions), _p(advance), _stream()), "sample")
     global _launches
     _launches += 1            # two kernels
+
+
+# ------------------------------------------------------------------------------------------------
+# Layer norm, depth-weighted average, xIELU, norms of slices, output gates
+def add_layernorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
+                  rows: Optional[torch.Tensor] = None, update: bool = True) -> None:
+    """As add_rmsnorm, with a layer norm (mean taken off, no bias): v = x[s] (+ delta[s], or the sum of its
+    partial sums); x[s] = v when update; out[r] = (v - mean) / sqrt(var + eps) * weight, s = rows[r] or r."""
+    _cuda(x, delta, weight, out, rows)
+    d = x.shape[1]
+    n = rows.numel() if rows is not None else x.shape[0]
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or not weight.is_contiguous():
+        raise KernelError("add_layernorm: x must be contiguous float32; out and weight contiguous")
+    if tuple(out.shape) != (n, d) or weight.numel() != d:
+        raise KernelError(f"add_layernorm: out is {tuple(out.shape)}, expected {(n, d)}; weight has {weight.numel()} of {d}")
+    parts, stride = 0, 0
+    if delta is not None:
+        parts, stride = _parts(delta, "add_layernorm: delta")
+        if tuple(delta.shape[-2:]) != tuple(x.shape) or not delta.is_contiguous():
+            raise KernelError("add_layernorm: delta must be contiguous and shaped like x")
+    if rows is not None:
+        _i32(rows, "rows")
+    with phase("layernorm"):
+        _check(lib().bg_add_layernorm(_p(x), _p(delta), _dt(delta) if delta is not None else F32, parts, stride, _p(weight),
+                                      _dt(weight), float(eps), _p(out), _dt(out), _p(rows), n, d, 1 if update else 0,
+                                      _stream()), "add_layernorm")
+
+
+def depth_mix(x: torch.Tensor, delta: Optional[torch.Tensor], history: torch.Tensor, weight: torch.Tensor, terms: int) -> None:
+    """v = x (+ delta or the sum of its partial sums); history[terms - 1] = v; x = sum_{j < terms} weight[j] history[j],
+    added in the order of j.  x float32 [T, d]; history float32 [slots >= terms, T, d]."""
+    _cuda(x, delta, history, weight)
+    if x.dtype != torch.float32 or history.dtype != torch.float32 or not x.is_contiguous() or not history.is_contiguous():
+        raise KernelError("depth_mix: x and history must be contiguous float32")
+    if history.dim() != 3 or tuple(history.shape[1:]) != tuple(x.shape) or not 1 <= terms <= history.shape[0]:
+        raise KernelError(f"depth_mix: history is {tuple(history.shape)} for {terms} terms of {tuple(x.shape)}")
+    if weight.numel() != terms or not weight.is_contiguous():
+        raise KernelError(f"depth_mix: {weight.numel()} weights for {terms} terms")
+    parts, stride = 0, 0
+    if delta is not None:
+        parts, stride = _parts(delta, "depth_mix: delta")
+        if tuple(delta.shape[-2:]) != tuple(x.shape) or not delta.is_contiguous():
+            raise KernelError("depth_mix: delta must be contiguous and shaped like x")
+    with phase("residuals"):
+        _check(lib().bg_depth_mix(_p(x), _p(delta), _dt(delta) if delta is not None else F32, parts, stride, _p(history),
+                                  x.numel(), _p(weight), _dt(weight), terms, x.numel(), _stream()), "depth_mix")
+
+
+def xielu(z: torch.Tensor, act: torch.Tensor, out: torch.Tensor) -> None:
+    """out = xIELU(z): with a_pos = softplus(act[0]) and a_neg = 1/2 + softplus(act[1]), z (a_pos z + 1/2) above zero
+    and a_neg (expm1(z) - z) + z/2 elsewhere.  z is [T, n] or float partial sums [parts, T, n]."""
+    _cuda(z, act, out)
+    parts, stride = _parts(z, "xielu: z")
+    if tuple(out.shape) != tuple(z.shape[-2:]) or not z.is_contiguous() or not out.is_contiguous() or act.numel() != 2:
+        raise KernelError("xielu: z [T, n] (or its partial sums), out [T, n], act with two numbers, all contiguous")
+    with phase("activation"):
+        _check(lib().bg_xielu(_p(z), _dt(z), parts, stride, _p(act), _dt(act), _p(out), _dt(out), out.numel(), _stream()), "xielu")
+
+
+def rmsnorm_slice(src: torch.Tensor, col0: int, n: int, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out[r] = RMS norm of src[r, col0 : col0 + n] times weight."""
+    _cuda(src, weight, out)
+    if src.dim() != 2 or src.stride(1) != 1 or col0 < 0 or col0 + n > src.shape[1]:
+        raise KernelError(f"rmsnorm_slice: columns {col0}..{col0 + n} of rows of {tuple(src.shape)}")
+    if tuple(out.shape) != (src.shape[0], n) or out.stride(1) != 1 or weight.numel() != n or not weight.is_contiguous():
+        raise KernelError("rmsnorm_slice: out is [rows, n] and weight has n values")
+    with phase("rmsnorm"):
+        _check(lib().bg_rmsnorm_slice(_p(src), _dt(src), src.stride(0), col0, n, _p(weight), _dt(weight), float(eps), _p(out),
+                                      _dt(out), out.stride(0), src.shape[0], _stream()), "rmsnorm_slice")
+
+
+def gate_heads(src: torch.Tensor, gate: torch.Tensor, gate_col0: int, out: torch.Tensor) -> None:
+    """out[t, h * vd + j] = src[h, t, j] * sigmoid(gate[t, gate_col0 + h]); src is [H, T, vd]."""
+    _cuda(src, gate, out)
+    H, T, vd = src.shape
+    if src.stride(2) != 1 or gate.stride(1) != 1 or gate_col0 + H > gate.shape[1] or gate.shape[0] < T:
+        raise KernelError("gate_heads: src [H, T, vd] with unit inner stride, gate rows that hold H values from gate_col0")
+    if tuple(out.shape) != (T, H * vd) or not out.is_contiguous():
+        raise KernelError(f"gate_heads: out is {tuple(out.shape)}, expected {(T, H * vd)}")
+    with phase("activation"):
+        _check(lib().bg_gate_heads(_p(src), _dt(src), src.stride(0), src.stride(1), _p(gate), _dt(gate), gate.stride(0),
+                                   gate_col0, _p(out), _dt(out), T, H, vd, _stream()), "gate_heads")
+
+
+def gemm_f32_nt_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[b] = a[b] @ w[b]^T for a [B, M, K], w [B, N, K], out [B, M, N], float32 views of any batch and row
+    strides with unit inner stride.  CUDA cores only."""
+    _cuda(a, w, out)
+    for t in (a, w, out):
+        if t.dtype != torch.float32 or t.dim() != 3 or t.stride(2) != 1:
+            raise KernelError("gemm_f32_nt_batched takes float32 [B, rows, cols] views with unit inner stride")
+    B, M, K = a.shape
+    N = w.shape[1]
+    if w.shape[0] != B or w.shape[2] != K or tuple(out.shape) != (B, M, N):
+        raise KernelError(f"gemm_f32_nt_batched: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not fit")
+    _check(lib().bg_gemm_f32_nt_batched(_p(a), a.stride(1), a.stride(0), _p(w), w.stride(1), w.stride(0), _p(out),
+                                        out.stride(1), out.stride(0), B, M, N, K, _stream()), "gemm_f32_nt_batched")
+
+
+# ------------------------------------------------------------------------------------------------
+# Attention through a latent
+def latent_attention_plan(rank: int, rot: int) -> Tuple[int, int]:
+    """(rows per CTA, keys per tile) of the latent attention kernel for a cache row of rank + rot features."""
+    rows, tile = _c_int(0), _c_int(0)
+    if lib().bg_latent_attention_plan(rank, rot, ctypes.byref(rows), ctypes.byref(tile)) != 0:
+        raise KernelError(f"latent attention: a cache row of {rank} + {rot} features does not fit a CTA's shared memory")
+    return rows.value, tile.value
+
+
+def latent_append(src: torch.Tensor, col0: int, rank: int, rot: int, rot_dims: int, weight: torch.Tensor, eps: float,
+                  cos_sin: Optional[torch.Tensor], positions: torch.Tensor, row_req: torch.Tensor,
+                  block_table: torch.Tensor, pool: torch.Tensor, status: Optional[torch.Tensor]) -> None:
+    """For every row t of src: pool[page, slot] = [rmsnorm(src[t, col0 : col0+rank]) * weight |
+    rotate(src[t, col0+rank : col0+rank+rot])] at positions[t] of request row_req[t]; pool is
+    [pages, page_size, rank + rot].  The first rot_dims features of the key part turn in pairs (2i, 2i+1) by
+    cos_sin [T, rot_dims/2, 2]."""
+    _cuda(src, weight, cos_sin, positions, row_req, block_table, pool, status)
+    _i32(positions, "positions"); _i32(row_req, "row_req"); _i32(block_table, "block_table")
+    T = positions.numel()
+    if src.dim() != 2 or src.stride(1) != 1 or src.shape[0] < T or col0 + rank + rot > src.shape[1]:
+        raise KernelError(f"latent_append: rows of {tuple(src.shape)} cannot hold {rank} + {rot} features from {col0}")
+    if pool.dim() != 3 or pool.shape[2] != rank + rot or not pool.is_contiguous():
+        raise KernelError(f"latent_append: the pool is {tuple(pool.shape)}, expected [pages, page, {rank + rot}]")
+    if weight.numel() != rank or not weight.is_contiguous():
+        raise KernelError("latent_append: one norm weight per latent feature")
+    if rot_dims > 0 and (cos_sin is None or cos_sin.dtype != torch.float32 or cos_sin.shape[0] < T
+                         or cos_sin.shape[1] != rot_dims // 2 or not cos_sin.is_contiguous()):
+        raise KernelError("latent_append: cos_sin must be float32 [T, rot_dims/2, 2]")
+    with phase("rope+kv_write"):
+        _check(lib().bg_latent_append(_p(src), _dt(src), src.stride(0), col0, rank, rot, rot_dims, _p(weight), _dt(weight),
+                                      float(eps), _p(cos_sin), _p(positions), _p(row_req), _p(block_table),
+                                      block_table.shape[1], _p(pool), _dt(pool), pool.shape[0], pool.shape[1], T, _p(status),
+                                      _stream()), "latent_append")
+
+
+def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, dim: int, rot: int, rot_dims: int,
+                     cos_sin: Optional[torch.Tensor], pool: torch.Tensor, block_table: torch.Tensor,
+                     positions: torch.Tensor, qblk: torch.Tensor, n_qblk: int, max_position: int, bq: int, hc: int,
+                     tile: int, split: int, scale: float, out: torch.Tensor, status: Optional[torch.Tensor]) -> None:
+    """Causal attention of a step's rows over the latent cache.  q_lat float32 [H, T, rank]: the queries carried into
+    the latent space; q_raw [T, H * (dim + rot)]: the query product's rows, whose rot part is rotated here; pool
+    [pages, page_size, rank + rot]; out [H, T, rank] receives, per head, the softmax-weighted sum of the cached
+    latents.  `qblk` is cut for `bq` rows; a CTA takes `hc` heads; keys are cut into splits of `split` positions."""
+    _cuda(q_lat, q_raw, cos_sin, pool, block_table, positions, qblk, out, status)
+    _i32(positions, "positions"); _i32(block_table, "block_table"); _i32(qblk, "qblk")
+    H, T, rank = q_lat.shape
+    if q_lat.dtype != torch.float32 or q_lat.stride(2) != 1 or tuple(out.shape) != (H, T, rank) or out.stride(2) != 1:
+        raise KernelError("latent_attention: q_lat float32 [H, T, rank] and out [H, T, rank] with unit inner stride")
+    if q_raw.dim() != 2 or q_raw.stride(1) != 1 or q_raw.shape[1] != H * (dim + rot) or q_raw.shape[0] < T:
+        raise KernelError(f"latent_attention: q_raw is {tuple(q_raw.shape)} for {H} heads of {dim} + {rot}")
+    if pool.dim() != 3 or pool.shape[2] != rank + rot or not pool.is_contiguous():
+        raise KernelError(f"latent_attention: the pool is {tuple(pool.shape)}, expected [pages, page, {rank + rot}]")
+    if rot_dims > 0 and (cos_sin is None or cos_sin.dtype != torch.float32 or cos_sin.shape[0] < T
+                         or cos_sin.shape[1] != rot_dims // 2 or not cos_sin.is_contiguous()):
+        raise KernelError("latent_attention: cos_sin must be float32 [T, rot_dims/2, 2]")
+    n_splits = max_position // split + 1
+    part_o = torch.empty((T * H * n_splits, rank), dtype=torch.float32, device=q_lat.device)
+    part_ml = torch.empty((T * H * n_splits, 2), dtype=torch.float32, device=q_lat.device)
+    L = lib()
+    with phase("attn"):
+        _check(L.bg_latent_attention_partial(_p(q_lat), _dt(q_lat), q_lat.stride(0), q_lat.stride(1), _p(q_raw), _dt(q_raw),
+                                             q_raw.stride(0), dim + rot, dim, _p(cos_sin), _p(pool), _dt(pool), pool.shape[0],
+                                             pool.shape[1], _p(block_table), block_table.shape[1], _p(positions), _p(qblk),
+                                             n_qblk, _p(part_o), _p(part_ml), n_splits, n_splits, H, hc, rank, rot, rot_dims,
+                                             split, tile, bq, float(scale), _p(status), _stream()), "latent_attention_partial")
+        _check(L.bg_latent_attention_merge(_p(part_o), _p(part_ml), _p(positions), _p(out), _dt(out), out.stride(0),
+                                           out.stride(1), T, H, rank, n_splits, split, _stream()), "latent_attention_merge")
+
+
+# ------------------------------------------------------------------------------------------------
+# The Mamba-2 recurrence
+def conv_silu(src: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,
+              conv_off: int, slots: torch.Tensor, row_req: torch.Tensor, reqs: torch.Tensor, n_req: int,
+              out: torch.Tensor) -> None:
+    """The causal convolution per channel with SiLU over src[:, col0 : col0 + channels], continued from and into the
+    slots' conv state.  weight [channels, taps] (last column the current token's), bias [channels]; state float32
+    [slots, slot size] with the conv state, (taps - 1) x channels, at conv_off; reqs int32 [n_req, 3] = (request,
+    first row, rows); out float32 [T, channels]."""
+    _cuda(src, weight, bias, state, slots, row_req, reqs, out)
+    _i32(slots, "slots"); _i32(row_req, "row_req"); _i32(reqs, "reqs")
+    T = row_req.numel()
+    taps = weight.shape[1]
+    if src.dim() != 2 or src.stride(1) != 1 or src.shape[0] < T or col0 + channels > src.shape[1]:
+        raise KernelError(f"conv_silu: rows of {tuple(src.shape)} cannot hold {channels} channels from {col0}")
+    if tuple(weight.shape) != (channels, taps) or bias.numel() != channels or weight.dtype != bias.dtype \
+            or not weight.is_contiguous() or not bias.is_contiguous():
+        raise KernelError("conv_silu: weight [channels, taps] and bias [channels] of one type")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or conv_off + (taps - 1) * channels > state.shape[1]:
+        raise KernelError(f"conv_silu: the state is {tuple(state.shape)}")
+    if out.dtype != torch.float32 or tuple(out.shape) != (T, channels) or not out.is_contiguous():
+        raise KernelError("conv_silu: out is float32 [T, channels]")
+    with phase("conv"):
+        _check(lib().bg_conv_silu(_p(src), _dt(src), src.stride(0), col0, channels, taps, _p(weight), _p(bias), _dt(weight),
+                                  _p(state), state.stride(0), conv_off, _p(slots), _p(row_req), _p(reqs), n_req, _p(out), T,
+                                  _stream()), "conv_silu")
+    if taps > 1:
+        count_launches(1)
+
+
+def ssm_scan(xbc: torch.Tensor, src: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor,
+             state: torch.Tensor, slots: torch.Tensor, reqs: torch.Tensor, n_req: int, y: torch.Tensor, H: int, P: int,
+             N: int, G: int) -> None:
+    """The recurrence over each request's rows, from and into the slots' state S [H, N, P] (float32, at the start of
+    a slot): dt = softplus(src[t, dt_col + h] + dt_bias[h]); S = exp(-exp(A_log[h]) dt) S + dt B_t x_t^T;
+    y_t = S^T C_t + D[h] x_t.  xbc float32 [T, H P + 2 G N] = [x | B | C]; y float32 [T, H P]."""
+    _cuda(xbc, src, dt_bias, A_log, D, state, slots, reqs, y)
+    _i32(slots, "slots"); _i32(reqs, "reqs")
+    T = xbc.shape[0]
+    if xbc.dtype != torch.float32 or not xbc.is_contiguous() or xbc.shape[1] != H * P + 2 * G * N:
+        raise KernelError(f"ssm_scan: xbc is {tuple(xbc.shape)}")
+    if src.dim() != 2 or src.stride(1) != 1 or dt_col + H > src.shape[1] or src.shape[0] < T:
+        raise KernelError("ssm_scan: the rows hold no step sizes there")
+    if not (dt_bias.dtype == A_log.dtype == D.dtype) or dt_bias.numel() != H or A_log.numel() != H or D.numel() != H:
+        raise KernelError("ssm_scan: dt_bias, A_log and D have one value per head, of one type")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < H * N * P:
+        raise KernelError(f"ssm_scan: the state is {tuple(state.shape)}")
+    if y.dtype != torch.float32 or tuple(y.shape) != (T, H * P) or not y.is_contiguous():
+        raise KernelError("ssm_scan: y is float32 [T, H P]")
+    with phase("scan"):
+        _check(lib().bg_ssm_scan(_p(xbc), xbc.shape[1], _p(src), _dt(src), src.stride(0), dt_col, _p(dt_bias), _p(A_log), _p(D),
+                                 _dt(D), _p(state), state.stride(0), _p(slots), _p(reqs), n_req, _p(y), H, P, N, G, _stream()),
+               "ssm_scan")
+
+
+def gated_group_rmsnorm(y: torch.Tensor, src: torch.Tensor, z_col: int, weight: torch.Tensor, eps: float, groups: int,
+                        out: torch.Tensor) -> None:
+    """out = RMS norm, in `groups` equal parts of a row, of y * silu(src[:, z_col : z_col + inner]), times weight."""
+    _cuda(y, src, weight, out)
+    T, inner = y.shape
+    if y.dtype != torch.float32 or not y.is_contiguous() or tuple(out.shape) != (T, inner) or not out.is_contiguous():
+        raise KernelError("gated_group_rmsnorm: y float32 [T, inner], out [T, inner]")
+    if src.dim() != 2 or src.stride(1) != 1 or z_col + inner > src.shape[1] or src.shape[0] < T or inner % groups:
+        raise KernelError("gated_group_rmsnorm: the gate's columns or the groups do not fit")
+    if weight.numel() != inner or not weight.is_contiguous():
+        raise KernelError("gated_group_rmsnorm: one weight per feature")
+    with phase("rmsnorm"):
+        _check(lib().bg_gated_group_rmsnorm(_p(y), _p(src), _dt(src), src.stride(0), z_col, _p(weight), _dt(weight), float(eps),
+                                            _p(out), _dt(out), T, inner, groups, _stream()), "gated_group_rmsnorm")

@@ -1,0 +1,209 @@
+// Small kernels around the residual stream and the activations that the Qwen2 parts do not have:
+// the centred norm (LayerNorm without a shift) with the residual add in front of it, the depth-weighted average of the layer results,
+// the xIELU activation, an RMS norm over a slice of a product's rows, and the per-head output gate.
+// All statistics and sums are float; every row's sums run in an order fixed by the sizes alone.
+#include "common.cuh"
+
+namespace bg {
+
+// For output row r (source row s = rows ? rows[r] : r):
+//   v = x[s] + sum_p delta[p][s];  if update: x[s] = v;
+//   out[r] = (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps) * w
+// One block per row; the row is held in shared memory between the passes (sum, squared deviations, output).
+template <typename TD, typename TW, typename TO>
+__global__ void add_layernorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int parts, size_t part_stride,
+                                     const TW* __restrict__ w, float eps, TO* __restrict__ out,
+                                     const int* __restrict__ rows, int d, int update) {
+    extern __shared__ float row_buf[];
+    __shared__ float red[32];
+    pdl_launch();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float* xr = x + (size_t)s * d;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = xr[i];
+        if (delta) v += sum_parts(delta + (size_t)s * d + i, parts, part_stride);
+        row_buf[i] = v;
+        if (update) xr[i] = v;
+        sum += v;
+    }
+    sum = block_sum(sum, red);
+    const float mean = sum / (float)d;
+    float sq = 0.0f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float dv = row_buf[i] - mean;
+        sq += dv * dv;
+    }
+    sq = block_sum(sq, red);
+    const float inv = 1.0f / sqrtf(sq / (float)d + eps);
+    TO* o = out + (size_t)r * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x)
+        o[i] = from_float<TO>((row_buf[i] - mean) * inv * to_float(w[i]));
+}
+
+// The depth-weighted average behind a layer.  With v = x + sum_p delta[p] (the layer's result):
+//   history[terms - 1] = v;   x = sum_{j < terms} w[j] * history[j], added in the order of j.
+// history is [slots][n] with hist_stride elements between slots; slots 0 .. terms-2 were written earlier.
+template <typename TD, typename TW>
+__global__ void depth_mix_kernel(float* __restrict__ x, const TD* __restrict__ delta, int parts, size_t part_stride,
+                                 float* __restrict__ history, size_t hist_stride, const TW* __restrict__ w, int terms,
+                                 size_t n) {
+    pdl_launch();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = x[i];
+    if (delta) v += sum_parts(delta + i, parts, part_stride);
+    history[(size_t)(terms - 1) * hist_stride + i] = v;
+    float acc = 0.0f;
+    for (int j = 0; j + 1 < terms; ++j) acc = fmaf(to_float(w[j]), history[(size_t)j * hist_stride + i], acc);
+    x[i] = fmaf(to_float(w[terms - 1]), v, acc);
+}
+
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
+
+// out = xIELU(z), z = in or the sum of its partial sums.  With a_pos = softplus(act[0]) and
+// a_neg = 1/2 + softplus(act[1]):   z > 0:  z (a_pos z + 1/2);    else:  a_neg (expm1(z) - z) + z/2
+template <typename TI, typename TW, typename TO>
+__global__ void xielu_kernel(const TI* __restrict__ in, int parts, size_t part_stride, const TW* __restrict__ act,
+                             TO* __restrict__ out, size_t n) {
+    pdl_launch();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float ap = softplus_f(to_float(act[0]));
+    const float an = 0.5f + softplus_f(to_float(act[1]));
+    const float z = parts > 1 ? sum_parts(in + i, parts, part_stride) : to_float(in[i]);
+    const float v = z > 0.0f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+    out[i] = from_float<TO>(v);
+}
+
+// out[r, 0..n) = s * rsqrt(mean(s^2) + eps) * w, s = src[r, col0 .. col0 + n): the RMS norm of a slice of
+// the rows of a product.  One block per row.
+template <typename TI, typename TW, typename TO>
+__global__ void rmsnorm_slice_kernel(const TI* __restrict__ src, int src_stride, int col0, int n,
+                                     const TW* __restrict__ w, float eps, TO* __restrict__ out, int out_stride) {
+    extern __shared__ float row_buf[];
+    __shared__ float red[32];
+    pdl_launch();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const TI* s = src + (size_t)r * src_stride + col0;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = to_float(s[i]);
+        row_buf[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+    TO* o = out + (size_t)r * out_stride;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_float<TO>(row_buf[i] * inv * to_float(w[i]));
+}
+
+// out[t, h * vd + j] = src[h][t][j] * sigmoid(gate[t, gate_col0 + h]): head-major results put row by row,
+// each head scaled by its gate.
+template <typename TI, typename TG, typename TO>
+__global__ void gate_heads_kernel(const TI* __restrict__ src, size_t src_head_stride, int src_row_stride,
+                                  const TG* __restrict__ gate, int gate_stride, int gate_col0, TO* __restrict__ out,
+                                  int T, int H, int vd) {
+    pdl_launch();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t n = (size_t)T * H * vd;
+    if (i >= n) return;
+    const int j = (int)(i % vd);
+    const int h = (int)((i / vd) % H);
+    const int t = (int)(i / ((size_t)vd * H));
+    const float g = to_float(gate[(size_t)t * gate_stride + gate_col0 + h]);
+    const float s = 1.0f / (1.0f + expf(-g));
+    out[i] = from_float<TO>(to_float(src[(size_t)h * src_head_stride + (size_t)t * src_row_stride + j]) * s);
+}
+
+}  // namespace bg
+
+using namespace bg;
+
+template <typename TD, typename TW>
+static int add_layernorm_out(float* x, const void* delta, int parts, size_t part_stride, const void* w, float eps, void* out,
+                             int out_dtype, const int* rows, int n_rows, int d, int update, cudaStream_t stream) {
+    const size_t smem = (size_t)d * sizeof(float);
+    if (smem > 200 * 1024) return BG_ERR_SHAPE;
+    BG_DISPATCH_DTYPE(out_dtype, TO, {
+        auto kern = add_layernorm_kernel<TD, TW, TO>;
+        if (smem > BG_SMEM_OPT_IN) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch(kern, dim3(n_rows), dim3(256), smem, stream, x, (const TD*)delta, parts, part_stride, (const TW*)w, eps,
+               (TO*)out, rows, d, update);
+    });
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+// The arguments of bg_add_rmsnorm, for the centred norm (scale vector, no shift).
+extern "C" int bg_add_layernorm(float* x, const void* delta, int delta_dtype, int parts, long long part_stride,
+                                const void* w, int w_dtype, float eps, void* out, int out_dtype, const int* rows,
+                                int n_rows, int d, int update, cudaStream_t stream) {
+    if (n_rows <= 0) return BG_OK;
+    if (!delta) { delta_dtype = BG_DTYPE_F32; parts = 0; }
+    BG_DISPATCH_DTYPE(delta_dtype, TD, BG_DISPATCH_DTYPE(w_dtype, TW,
+        return (add_layernorm_out<TD, TW>(x, delta, parts, (size_t)part_stride, w, eps, out, out_dtype, rows, n_rows, d,
+                                          update, stream))));
+    return BG_OK;
+}
+
+extern "C" int bg_depth_mix(float* x, const void* delta, int delta_dtype, int parts, long long part_stride, float* history,
+                            long long hist_stride, const void* w, int w_dtype, int terms, long long n, cudaStream_t stream) {
+    if (n <= 0) return BG_OK;
+    if (terms < 1) return BG_ERR_SHAPE;
+    if (!delta) { delta_dtype = BG_DTYPE_F32; parts = 0; }
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    BG_DISPATCH_DTYPE(delta_dtype, TD, BG_DISPATCH_DTYPE(w_dtype, TW,
+        launch(depth_mix_kernel<TD, TW>, dim3(blocks), dim3(256), 0, stream, x, (const TD*)delta, parts, (size_t)part_stride,
+               history, (size_t)hist_stride, (const TW*)w, terms, (size_t)n)));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_xielu(const void* in, int in_dtype, int parts, long long part_stride, const void* act, int act_dtype,
+                        void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return BG_OK;
+    if (parts > 1 && in_dtype != BG_DTYPE_F32) return BG_ERR_DTYPE;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    BG_DISPATCH_DTYPE(in_dtype, TI, BG_DISPATCH_DTYPE(act_dtype, TW, BG_DISPATCH_DTYPE(out_dtype, TO,
+        launch(xielu_kernel<TI, TW, TO>, dim3(blocks), dim3(256), 0, stream, (const TI*)in, parts, (size_t)part_stride,
+               (const TW*)act, (TO*)out, (size_t)n))));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_rmsnorm_slice(const void* src, int src_dtype, int src_stride, int col0, int n, const void* w, int w_dtype,
+                                float eps, void* out, int out_dtype, int out_stride, int rows, cudaStream_t stream) {
+    if (rows <= 0) return BG_OK;
+    if (n <= 0) return BG_ERR_SHAPE;
+    const size_t smem = (size_t)n * sizeof(float);
+    if (smem > 200 * 1024) return BG_ERR_SHAPE;
+    const int threads = n >= 256 ? 256 : (n + 31) / 32 * 32;
+    BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(w_dtype, TW, BG_DISPATCH_DTYPE(out_dtype, TO, {
+        auto kern = rmsnorm_slice_kernel<TI, TW, TO>;
+        if (smem > BG_SMEM_OPT_IN) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch(kern, dim3(rows), dim3(threads), smem, stream, (const TI*)src, src_stride, col0, n, (const TW*)w, eps, (TO*)out,
+               out_stride);
+    })));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_gate_heads(const void* src, int src_dtype, long long src_head_stride, int src_row_stride, const void* gate,
+                             int gate_dtype, int gate_stride, int gate_col0, void* out, int out_dtype, int T, int H, int vd,
+                             cudaStream_t stream) {
+    const long long n = (long long)T * H * vd;
+    if (n <= 0) return BG_OK;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(gate_dtype, TG, BG_DISPATCH_DTYPE(out_dtype, TO,
+        launch(gate_heads_kernel<TI, TG, TO>, dim3(blocks), dim3(256), 0, stream, (const TI*)src, (size_t)src_head_stride,
+               src_row_stride, (const TG*)gate, gate_stride, gate_col0, (TO*)out, T, H, vd))));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}

@@ -83,10 +83,12 @@ class DecoderModel:
         return total
 
     # ------------------------------------------------------------------ forward
-    def forward(self, batch, cache) -> Optional[torch.Tensor]:
+    def forward(self, batch, cache, tap=None) -> Optional[torch.Tensor]:
         """Run the batch's rows through every stage, from and into `cache`; return float logits
         [wanted rows, vocab], or None when no row's logits are wanted (the head is skipped then, as
-        qwen_infer.c:2145 skips it)."""
+        qwen_infer.c:2145 skips it).  `tap(stage, rows)` is called behind every stage with a copy of the
+        float residual stream [T, hidden] as that stage leaves it (for looking into a model layer by layer; it
+        reads what the stream still owes, so it is not for captured steps)."""
         x = torch.empty((batch.n_rows, self.spec.hidden), dtype=torch.float32, device=self.ctx.device)
         ops.embed_gather(self.embed, batch.token_ids, x, self.ctx.status, scale=self.spec.embed_scale)
         stream = ResidualStream(x)
@@ -94,6 +96,11 @@ class DecoderModel:
             owner = si if stage.cache is None else stage.cache
             view = cache.view(owner, batch) if owner in cache.stage_group else None
             self.blocks[stage.layer].forward(stream, batch, view)
+            if tap is not None:
+                rows = stream.x.clone()
+                if stream.pending is not None:
+                    rows += stream.pending.float().reshape(-1, *rows.shape).sum(0)
+                tap(si, rows)
         if batch.n_logit_rows == 0:
             return None
         h = self.final_norm.add_norm(stream.x, stream.pending, rows=batch.logit_rows, update=False)

@@ -3,7 +3,8 @@ h = norm(x); x += mixer(h); h = norm(x); x += feed_forward(h)  (qwen_infer.c:144
 :1577).  The residual x is float.  A block does not add its last result to x itself: it returns it,
 and the next norm (of the next block, or the final one) adds it, fused with its statistics; or, in
 steps of few tokens, the part's last product adds it and the next part's first product norms (see
-stream.py)."""
+stream.py).  The other kinds are the same layer without a feed-forward, and either with a combiner
+behind it: a part that rewrites the stream from the results of this and earlier layers."""
 from __future__ import annotations
 
 from .registry import register_block
@@ -16,14 +17,18 @@ class PreNormBlock:
     # block is constructed with one keyword argument per slot.
     SLOTS = (("mixer_norm", "norm"), ("mixer", "mixer"), ("feed_forward_norm", "norm"), ("feed_forward", "feed_forward"))
 
-    def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward):
+    def __init__(self, mixer_norm, mixer, feed_forward_norm=None, feed_forward=None, combiner=None):
         self.mixer_norm, self.mixer = mixer_norm, mixer
         self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
+        self.combiner = combiner
 
     def forward(self, stream: ResidualStream, batch, cache) -> None:
         """Runs the layer on the residual stream.  A part that declares `takes_stream` gets the norm of the
         stream uncomputed (its first product may apply it) and the stream itself (its last product may add
-        to it); any other part gets the normed rows and returns its addend, which the stream then owes."""
+        to it); any other part gets the normed rows and returns its addend, which the stream then owes.
+        A combiner sees the stream before the sublayers (`begin`) and rewrites it behind them (`forward`)."""
+        if self.combiner is not None:
+            self.combiner.begin(stream)
         h = NormedInput(stream, self.mixer_norm)
         if getattr(self.mixer, "takes_stream", False):
             a = self.mixer.forward(h, batch, cache, stream)
@@ -31,10 +36,30 @@ class PreNormBlock:
             a = self.mixer.forward(h.tensor(), batch, cache)
         if a is not None:
             stream.owe(a)
-        h = NormedInput(stream, self.feed_forward_norm)
-        if getattr(self.feed_forward, "takes_stream", False):
-            m = self.feed_forward.forward(h, batch, stream)
-        else:
-            m = self.feed_forward.forward(h.tensor(), batch)
-        if m is not None:
-            stream.owe(m)
+        if self.feed_forward is not None:
+            h = NormedInput(stream, self.feed_forward_norm)
+            if getattr(self.feed_forward, "takes_stream", False):
+                m = self.feed_forward.forward(h, batch, stream)
+            else:
+                m = self.feed_forward.forward(h.tensor(), batch)
+            if m is not None:
+                stream.owe(m)
+        if self.combiner is not None:
+            self.combiner.forward(stream, batch)
+
+
+@register_block("prenorm_mixer")
+class PreNormMixerBlock(PreNormBlock):
+    """A layer without a feed-forward: x += mixer(norm(x)) and nothing else."""
+    SLOTS = (("mixer_norm", "norm"), ("mixer", "mixer"))
+
+
+@register_block("prenorm_combined")
+class PreNormCombinedBlock(PreNormBlock):
+    """The pre-norm layer with a combiner behind it (e.g. the depth-weighted average of the layer results)."""
+    SLOTS = PreNormBlock.SLOTS + (("combiner", "combiner"),)
+
+
+@register_block("prenorm_mixer_combined")
+class PreNormMixerCombinedBlock(PreNormBlock):
+    SLOTS = PreNormMixerBlock.SLOTS + (("combiner", "combiner"),)

@@ -19,6 +19,24 @@ class PagedKVNeed:
     head_dim: int
     window: Optional[int] = None
 
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        """What one page of one stage holds: (2 = keys, values; kv heads; positions; features)."""
+        return (2, self.n_kv_heads, page_size, self.head_dim)
+
+
+@dataclass(frozen=True)
+class PagedLatentNeed:
+    """ONE row of `width` features per position, shared by all heads (the latent of an attention that makes
+    its keys and values from a low-rank projection, with whatever rides along, such as a rotated key part)."""
+    width: int
+    window: Optional[int] = None
+
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        return (page_size, self.width)
+
+
+PAGED_NEEDS = (PagedKVNeed, PagedLatentNeed)
+
 
 @dataclass(frozen=True)
 class FixedStateNeed:
@@ -29,8 +47,9 @@ class FixedStateNeed:
 
 @dataclass
 class PagedKVView:
-    """One stage's pages, [num_pages, 2, n_kv_heads, page_size, head_dim] (2 = keys, values), and
-    the step's block table [requests, max_pages] (int32, -1 where no page is held)."""
+    """One stage's pages, [num_pages, 2, n_kv_heads, page_size, head_dim] (2 = keys, values) for keys and values
+    or [num_pages, page_size, width] for a latent, and the step's block table [requests, max_pages] (int32, -1
+    where no page is held)."""
     pool: torch.Tensor
     block_table: torch.Tensor
     page_size: int

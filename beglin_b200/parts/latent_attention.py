@@ -1,0 +1,118 @@
+"""Attention through a low-rank latent, with an output gate per head.
+
+Of every position only ONE row is cached for all heads: the RMS-normed latent c (kv_rank features) and the
+rotated key part k_r (rot_dim features) that the heads share.  A head's keys W_uk c and values W_uv c are
+never made.  Since q . (W_uk c) = (W_uk^T q) . c, the un-rotated part of a query is carried into the latent
+space (one small product per head), the attention kernel scores it against the cached c directly and
+returns, per head, the softmax-weighted sum of the c, and W_uv is applied to that sum (again one small
+product per head).  So a step never touches more of the cache than the cached rows themselves, whatever the
+number of heads.
+
+A step: ONE product of the mixer's input for the query latent, the key/value latent with the key part and
+the gates (the matrices are concatenated at load time); norm of the query latent; norm, rotation and append
+of the key/value latent; the query product; queries into the latent space; attention; values out of the
+latent space; gates; the output product.  A mixer with `own_kv` False has no key/value projection and reads
+the cache of the stage it is told to.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..csrc import ops
+from .cache_need import PagedKVView, PagedLatentNeed
+from .context import BuildContext
+from .linear import Linear
+from .registry import register_mixer
+from .rope import shared_position
+from .spec import LatentAttentionSpec, TensorRole
+
+
+@register_mixer("latent_attention")
+class LatentAttention:
+    @staticmethod
+    def expected_tensors(spec: LatentAttentionSpec) -> List[TensorRole]:
+        H, qd = spec.n_heads, spec.dim + spec.rot_dim
+        roles = [TensorRole("q_down.weight", (spec.q_rank, spec.hidden), True, True),
+                 TensorRole("q_down.norm", (spec.q_rank,), role="scale"),
+                 TensorRole("q_up.weight", (H * qd, spec.q_rank), True, True),
+                 TensorRole("k_up.weight", (H * spec.dim, spec.kv_rank), True, True),
+                 TensorRole("v_up.weight", (H * spec.vdim, spec.kv_rank), True, True),
+                 TensorRole("o_proj.weight", (spec.hidden, H * spec.vdim), True, True)]
+        if spec.own_kv:
+            roles += [TensorRole("kv_down.weight", (spec.kv_rank + spec.rot_dim, spec.hidden), True, True),
+                      TensorRole("kv_down.norm", (spec.kv_rank,), role="scale")]
+        if spec.gated:
+            roles.append(TensorRole("gate.weight", (H, spec.hidden), True, True))
+        return roles
+
+    @staticmethod
+    def cache_need(spec: LatentAttentionSpec) -> Optional[PagedLatentNeed]:
+        if not spec.own_kv:
+            return None
+        return PagedLatentNeed(spec.kv_rank + spec.rot_dim)
+
+    def __init__(self, spec: LatentAttentionSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
+        self.spec, self.ctx = spec, ctx
+        H = spec.n_heads
+        self.position = shared_position(spec.position, ctx)
+        self.rot_dims = int(self.position.rotary_dim)
+        if self.rot_dims > spec.rot_dim or (self.rot_dims and not self.position.interleaved):
+            raise ValueError(f"the rotated part of {spec.rot_dim} features turns in neighbouring pairs over at most "
+                             f"its own width, not {self.rot_dims} features paired '{spec.position.pairing}'")
+        # the products of the mixer's input, as ONE: [query latent | key/value latent, key part | gates]
+        names = ["q_down.weight"] + (["kv_down.weight"] if spec.own_kv else []) + (["gate.weight"] if spec.gated else [])
+        self.down = Linear(torch.cat([tensors[n] for n in names], dim=0), None, ctx, label="proj_qkv")
+        self.kv_col = spec.q_rank
+        self.gate_col = spec.q_rank + (spec.kv_rank + spec.rot_dim if spec.own_kv else 0)
+        self.q_norm = ctx.vector(tensors["q_down.norm"])
+        self.kv_norm = ctx.vector(tensors["kv_down.norm"]) if spec.own_kv else None
+        self.q_up = Linear(tensors["q_up.weight"], None, ctx, label="proj_q")
+        # per head: W_uk^T as [kv_rank, dim] (the product into the latent space is x W^T with W = W_uk^T) and
+        # W_uv as [vdim, kv_rank]
+        self.k_up_t = ctx.matrix(tensors["k_up.weight"].reshape(H, spec.dim, spec.kv_rank).transpose(1, 2))
+        self.v_up = ctx.matrix(tensors["v_up.weight"].reshape(H, spec.vdim, spec.kv_rank))
+        self.o_proj = Linear(tensors["o_proj.weight"], None, ctx, label="proj_o")
+        self.scale = float(np.float32(spec.scale))
+        rows, self.tile = ops.latent_attention_plan(spec.kv_rank, spec.rot_dim)
+        self.hc = min(H, rows)                      # heads per CTA
+        self.bq = max(1, rows // self.hc)           # rows of one request per CTA
+        self.f32 = ctx.compute_dtype == torch.float32
+
+    def _per_head(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """out[h] = x[h] @ w[h]^T for x [H, T, K] (a view of any strides) and w [H, N, K]: [H, T, N]."""
+        H, T, _ = x.shape
+        if self.f32:
+            out = torch.empty((H, T, w.shape[1]), dtype=torch.float32, device=x.device)
+            ops.gemm_f32_nt_batched(x, w, out)
+            return out
+        with ops.phase("proj_heads"):
+            return torch.bmm(x, w.transpose(1, 2), out_dtype=out_dtype)
+
+    def forward(self, h: torch.Tensor, batch, cache: PagedKVView) -> torch.Tensor:
+        s, ctx = self.spec, self.ctx
+        T, H = batch.n_rows, s.n_heads
+        down = self.down(h, out_dtype=torch.float32)                    # [T, q_rank (+ kv_rank + rot) (+ H)]
+        cos_sin = self.position.table(batch) if self.rot_dims else None
+        if s.own_kv:
+            ops.latent_append(down, self.kv_col, s.kv_rank, s.rot_dim, self.rot_dims, self.kv_norm, s.eps, cos_sin,
+                              batch.positions, batch.row_req, cache.block_table, cache.pool, ctx.status)
+        cq = torch.empty((T, s.q_rank), dtype=ctx.compute_dtype, device=h.device)
+        ops.rmsnorm_slice(down, 0, s.q_rank, self.q_norm, s.eps, cq)
+        q = self.q_up(cq)                                               # [T, H (dim + rot)]
+        q_plain = q.view(T, H, s.dim + s.rot_dim)[:, :, :s.dim].transpose(0, 1)          # [H, T, dim]
+        q_lat = self._per_head(q_plain, self.k_up_t, torch.float32)    # [H, T, kv_rank] float
+        qblk, n_qblk = batch.query_blocks(self.bq)
+        o_lat = torch.empty((H, T, s.kv_rank), dtype=ctx.compute_dtype, device=h.device)
+        ops.latent_attention(q_lat, q, s.dim, s.rot_dim, self.rot_dims, cos_sin, cache.pool, cache.block_table,
+                             batch.positions, qblk, n_qblk, batch.max_position, self.bq, self.hc, self.tile, ctx.kv_split,
+                             self.scale, o_lat, ctx.status)
+        v = self._per_head(o_lat, self.v_up, ctx.compute_dtype)        # [H, T, vdim]
+        out = torch.empty((T, H * s.vdim), dtype=ctx.compute_dtype, device=h.device)
+        if s.gated:
+            ops.gate_heads(v, down, self.gate_col, out)
+        else:
+            out.view(T, H, s.vdim).copy_(v.transpose(0, 1))
+        return self.o_proj.partial(out)

@@ -11,7 +11,7 @@ from ..csrc import ops
 from .context import BuildContext
 from .linear import Linear
 from .registry import register_feed_forward
-from .spec import SwiGLUSpec, TensorRole
+from .spec import DenseActSpec, SwiGLUSpec, TensorRole
 from .stream import ResidualStream
 
 
@@ -51,3 +51,30 @@ class SwiGLU:
             return self.down.partial(act)
         self.down.into(act, stream)
         return None
+
+
+@register_feed_forward("dense_act")
+class DenseAct:
+    """m = W_down act(W_up h): one hidden layer without a gate branch.  The activation (xIELU) is a kernel of its
+    own between the two products; it reads the up product's result (or its partial sums) as floats and writes
+    the compute type."""
+
+    @staticmethod
+    def expected_tensors(spec: DenseActSpec) -> List[TensorRole]:
+        return [TensorRole("up.weight", (spec.intermediate, spec.hidden), True, True),
+                TensorRole("down.weight", (spec.hidden, spec.intermediate), True, True),
+                TensorRole("act", (2,))]
+
+    def __init__(self, spec: DenseActSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
+        if spec.activation != "xielu":
+            raise ValueError(f"unknown activation '{spec.activation}' of a dense feed-forward")
+        self.spec, self.ctx = spec, ctx
+        self.up = Linear(tensors["up.weight"], None, ctx, label="proj_up")
+        self.down = Linear(tensors["down.weight"], None, ctx, label="proj_down")
+        self.act = ctx.vector(tensors["act"])
+
+    def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
+        z = self.up.partial(h)
+        a = torch.empty((h.shape[0], self.spec.intermediate), dtype=self.ctx.compute_dtype, device=h.device)
+        ops.xielu(z, self.act, a)
+        return self.down.partial(a)

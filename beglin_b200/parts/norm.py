@@ -1,6 +1,7 @@
 """RMSNorm: y = x / sqrt(mean(x^2) + eps) * weight, statistics in float, eps inside the root, the
 weight multiplying directly (qwen_infer.c:711-714).  The residual add that precedes a norm is fused
-into it: `add_norm` first does x += delta."""
+into it: `add_norm` first does x += delta.  LayerNorm is the same with the mean taken off first and
+the variance in place of the mean square; it has a scale vector and no shift."""
 from __future__ import annotations
 
 from typing import Dict, List, Optional
@@ -38,3 +39,22 @@ class RMSNorm:
         if self.weight.dtype != self.ctx.compute_dtype:
             return None
         return self.weight, float(self.spec.eps)
+
+
+@register_norm("layernorm")
+class LayerNorm:
+    @staticmethod
+    def expected_tensors(spec: NormSpec) -> List[TensorRole]:
+        return [TensorRole("weight", (spec.size,), role="scale")]
+
+    def __init__(self, spec: NormSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
+        self.spec, self.ctx = spec, ctx
+        self.weight = ctx.vector(tensors["weight"])
+
+    def add_norm(self, x: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
+                 update: bool = True) -> torch.Tensor:
+        """As RMSNorm.add_norm: x += delta (when given and `update`), then the normed rows in the compute type."""
+        n = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.spec.size), dtype=self.ctx.compute_dtype, device=x.device)
+        ops.add_layernorm(x, delta, self.weight, self.spec.eps, out, rows=rows, update=update and rows is None)
+        return out

@@ -13,6 +13,7 @@ FEED_FORWARDS: Dict[str, type] = {}
 NORMS: Dict[str, type] = {}
 POSITIONS: Dict[str, type] = {}
 BLOCKS: Dict[str, type] = {}
+COMBINERS: Dict[str, type] = {}      # what a block does to the stream behind its sublayers (depth averages)
 
 
 def _register(table: Dict[str, type], what: str) -> Callable[[str], Callable[[type], type]]:
@@ -30,6 +31,7 @@ register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_norm = _register(NORMS, "norm")
 register_position = _register(POSITIONS, "position encoding")
 register_block = _register(BLOCKS, "block")
+register_combiner = _register(COMBINERS, "combiner")
 
 
 def lookup(table: Dict[str, type], kind: str, what: str) -> type:
@@ -60,7 +62,8 @@ def block_class(kind: str) -> type:
     return lookup(BLOCKS, kind, "block")
 
 
-FAMILIES = {"mixer": (MIXERS, "mixer"), "feed_forward": (FEED_FORWARDS, "feed-forward"), "norm": (NORMS, "norm")}
+FAMILIES = {"mixer": (MIXERS, "mixer"), "feed_forward": (FEED_FORWARDS, "feed-forward"), "norm": (NORMS, "norm"),
+            "combiner": (COMBINERS, "combiner")}
 
 
 def part_class(family: str, kind: str) -> type:

@@ -18,7 +18,8 @@ class TensorRole:
     whether it is a matrix of a matrix product (kept in the compute dtype) or a small vector or
     table (kept as stored), and what it is for.  `role` decides how random weights are drawn:
     "matrix" and "vector" around zero, "bias" around zero with a deviation of its own, "scale" (a
-    norm's weight, which multiplies) around one.  Empty means "matrix" or "vector" by `matrix`."""
+    norm's weight, which multiplies) around one, "average" (the weights of a sum whose last term is the main
+    one) around zero with the last around one.  Empty means "matrix" or "vector" by `matrix`."""
     name: str
     shape: Tuple[int, ...]
     required: bool = True
@@ -31,6 +32,8 @@ class TensorRole:
 
 @dataclass(frozen=True)
 class NormSpec:
+    """kind "rmsnorm": x * rsqrt(mean(x^2) + eps) * w.  kind "layernorm": centred first,
+    c = x - mean(x), then c * rsqrt(mean(c^2) + eps) * w; there is no shift vector."""
     size: int
     eps: float
     kind: str = "rmsnorm"
@@ -72,6 +75,65 @@ class SwiGLUSpec:
     hidden: int
     intermediate: int
     kind: str = "swiglu"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose keys and values are made from a cached low-rank latent.  Per head `dim` features that
+    are not rotated and `rot_dim` that are (queries), the rotated key part being ONE vector shared by all
+    heads; values of `vdim` features; the queries pass a latent of `q_rank` features, keys and values one of
+    `kv_rank`.  `position.rotary_dim` leading features of the rot part turn.  Each head's result is scaled by
+    sigmoid of a per-head gate read from the mixer's input when `gated`.  `own_kv` False: no down-projection
+    of its own; the latent and key part of another stage's cache are read."""
+    hidden: int
+    n_heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    eps: float
+    position: PositionSpec
+    gated: bool = True
+    own_kv: bool = True
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class Mamba2Spec:
+    """The Mamba-2 recurrence: `n_heads` heads of `vdim` features with a state of `state` x vdim each, B and C
+    shared inside each of `groups` groups of heads, a causal convolution of `conv` taps over x, B and C, and
+    an RMS norm of the gated result in `norm_groups` equal parts."""
+    hidden: int
+    n_heads: int
+    vdim: int
+    state: int
+    groups: int
+    conv: int
+    norm_groups: int
+    eps: float
+    kind: str = "mamba2"
+
+
+@dataclass(frozen=True)
+class DenseActSpec:
+    """Feed-forward with one hidden layer, down(act(up(h))), no gate branch.  `activation` "xielu": a parabola
+    above zero and a scaled exponential below, with two learned numbers."""
+    hidden: int
+    intermediate: int
+    activation: str = "xielu"
+    kind: str = "dense_act"
+
+
+@dataclass(frozen=True)
+class DepthAverageSpec:
+    """Behind a layer the stream is replaced by a learned weighted sum of the embedded rows and every layer's
+    result up to this one: `terms` of them for this layer (its own result is the last), out of `total` in the
+    model."""
+    terms: int
+    total: int
+    kind: str = "depth_average"
 
 
 class LayerSpec:

@@ -20,6 +20,8 @@ class ResidualStream:
         self.x = x                                     # float32 [T, d]
         self.pending: Optional[torch.Tensor] = None    # not yet added to x: [T, d] or partial sums [parts, T, d]
         self.ssq: Optional[torch.Tensor] = None        # float32 [parts, >= T]: partial sums of squares of x's rows
+        self.history: Optional[torch.Tensor] = None    # float32 [slots, T, d]: the embedding output and the layer
+        #                                                results so far, kept by a combiner that mixes over depth
 
     def owe(self, addend: torch.Tensor) -> None:
         self.pending, self.ssq = addend, None

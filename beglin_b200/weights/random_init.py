@@ -1,7 +1,8 @@
 """Random weights for a configuration: in memory, or as a model folder (config.json and
 model.safetensors) that every loader of the framework reads like a downloaded one.
 
-Matrices and biases are N(0, std) and N(0, bias_std); norm weights are 1 + N(0, norm_std); which
+Matrices and biases are N(0, std) and N(0, bias_std); norm weights are 1 + N(0, norm_std); the weights of
+an average over depth are N(0, std) with 1 added to the last; which
 of these a tensor is says the `role` of the part's `TensorRole`, never its name.  Each
 tensor has a generator of its own, seeded from (seed, tensor name), so the values do not depend on
 the order or on which other tensors exist.  The reference has no such mode in its engine; its tests
@@ -58,6 +59,8 @@ def random_tensors(spec: ModelSpec, seed: int, std: float = 0.02, bias_std: Opti
             kind = role.init_role()
             mean, scale = (1.0, norm_std) if kind == "scale" else (0.0, bias_std if kind == "bias" else std)
             out[name] = _counter_tensor(name, role, seed, mean, scale, dtype, device)
+            if kind == "average":
+                out[name].reshape(-1)[-1] += 1.0
             continue
         gen = torch.Generator(device=device)
         gen.manual_seed((int(seed) * 1000003 + zlib.crc32(name.encode())) % (2**63))
@@ -74,6 +77,9 @@ def random_tensors(spec: ModelSpec, seed: int, std: float = 0.02, bias_std: Opti
         x = torch.randn(role.shape, generator=gen, dtype=torch.float32, device=device)
         if kind == "scale":
             x = 1.0 + norm_std * x
+        elif kind == "average":            # a weighted sum that mostly passes its last term on
+            x = std * x
+            x.reshape(-1)[-1] += 1.0
         elif kind == "bias":
             x = bias_std * x
         else:

@@ -43,7 +43,7 @@ def silu(z: torch.Tensor) -> torch.Tensor:
 
 
 def rms_unit(x: torch.Tensor, eps: float) -> torch.Tensor:
-    """x divided by its root mean square over the last axis, eps inside the root."""
+    """x * rsqrt(mean(x^2) + eps) along the last axis."""
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
 
@@ -56,7 +56,7 @@ def layer_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def xielu(z: torch.Tensor, p: torch.Tensor, q: torch.Tensor) -> torch.Tensor:
-    """Above zero a parabola softplus(p) z^2 + z/2; at and below zero (1/2 + softplus(q)) (e^z - 1 - z) + z/2."""
+    """A parabola through the origin above zero, a scaled exponential below; both branches have slope 1/2 at 0."""
     ap = softplus(p)
     an = 0.5 + softplus(q)
     pos = ap * z * z + 0.5 * z
@@ -122,13 +122,13 @@ def latent_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dic
 
 # ----------------------------------------------------------------------------- Mamba-2
 def mamba2(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float) -> torch.Tensor:
-    """h [T, width] of ONE sequence from its position 0; the state starts at zero."""
+    """h [T, width] of ONE sequence from its position 0, with S = 0 before the first token."""
     T = h.shape[0]
     H, P, N, G, taps = m["heads"], m["vdim"], m["state"], m["groups"], m["conv"]
     inner = H * P
     proj = h @ w[p + "mix.in"].t()
     z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N:]
-    # causal convolution per channel: tap j multiplies the input taps-1-j tokens back, zeros before the start
+    # causal convolution per channel: tap j multiplies the input taps-1-j tokens back; nothing precedes token 0
     cw, cb = w[p + "mix.conv"], w[p + "mix.conv.b"]
     conv = torch.zeros_like(xbc)
     for t in range(T):
