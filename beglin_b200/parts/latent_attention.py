@@ -89,6 +89,8 @@ class LatentAttention:
             ops.gemm_f32_nt_batched(x, w, out)
             return out
         with ops.phase("proj_heads"):
+            if out_dtype == x.dtype:
+                return torch.bmm(x, w.transpose(1, 2))
             return torch.bmm(x, w.transpose(1, 2), out_dtype=out_dtype)
 
     def forward(self, h: torch.Tensor, batch, cache: PagedKVView) -> torch.Tensor:
@@ -105,6 +107,9 @@ class LatentAttention:
         q_plain = q.view(T, H, s.dim + s.rot_dim)[:, :, :s.dim].transpose(0, 1)          # [H, T, dim]
         q_lat = self._per_head(q_plain, self.k_up_t, torch.float32)    # [H, T, kv_rank] float
         qblk, n_qblk = batch.query_blocks(self.bq)
+        if qblk is None:                                                # a decoding graph's batch keeps its list implicit
+            batch.implicit_blocks = False
+            qblk, n_qblk = batch.query_blocks(self.bq)
         o_lat = torch.empty((H, T, s.kv_rank), dtype=ctx.compute_dtype, device=h.device)
         ops.latent_attention(q_lat, q, s.dim, s.rot_dim, self.rot_dims, cos_sin, cache.pool, cache.block_table,
                              batch.positions, qblk, n_qblk, batch.max_position, self.bq, self.hc, self.tile, ctx.kv_split,

@@ -7,6 +7,7 @@ This test calls it twice in a row, with different inputs, and wants the same tok
 entry point (whose scratch the caller allocates) gives; tokens are integers, so "the same" is exact.
 The file sorts last so that a run that stops at the first failure has run everything else before."""
 import ctypes
+import gc
 
 import pytest
 import torch
@@ -46,6 +47,7 @@ def test_no_alloc_sampling_matches_the_ordinary_entry_point_twice_in_a_row():
         want = torch.empty(n, dtype=torch.int32, device=DEV)
         ops.sample(logits, temperature, uniform, want)
         got = torch.full((n,), -1, dtype=torch.int32, device=DEV)
+        gc.collect()                                             # what earlier tests dropped in cycles goes now, not during the call
         before = torch.cuda.memory_allocated()
         rc, msg = call(fn, logits, temperature, uniform, got)
         assert rc == 0, msg
