@@ -160,10 +160,22 @@ latent_attention_partial_kernel(LatentParams p) {
             base_s[j] = off;
         }
         __syncthreads();
-        for (int idx = tid; idx < tile * width; idx += LAT_THREADS) {
-            const int j = idx / width, d = idx - j * width;
+        // a warp per key row, four loads of a lane on their way at a time (a load that waited for the store of the
+        // one before it left the kernel bound by the latency of single loads)
+        for (int j = warp; j < tile; j += LAT_WARPS) {
             const long long off = base_s[j];
-            k_s[j * kstride + d] = off >= 0 ? to_float(pool[off + d]) : 0.0f;
+            float* dst = k_s + j * kstride;
+            if (off < 0) {
+                for (int d = lane; d < width; d += 32) dst[d] = 0.0f;
+                continue;
+            }
+            const TC* srow = pool + off;
+            int d = lane;
+            for (; d + 96 < width; d += 128) {
+                const TC a0 = srow[d], a1 = srow[d + 32], a2 = srow[d + 64], a3 = srow[d + 96];
+                dst[d] = to_float(a0); dst[d + 32] = to_float(a1); dst[d + 64] = to_float(a2); dst[d + 96] = to_float(a3);
+            }
+            for (; d < width; d += 32) dst[d] = to_float(srow[d]);
         }
         __syncthreads();
 
@@ -181,9 +193,16 @@ latent_attention_partial_kernel(LatentParams p) {
                     const int key = t0 + j;
                     if (key <= pos && key < k_end && base_s[j] >= 0) {
                         const float* kr = k_s + j * kstride;
-                        float dot = 0.0f;
-                        for (int d = 0; d < width; ++d) dot = fmaf(qrow[d], kr[d], dot);
-                        s[c] = dot * p.scale;
+                        float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;      // four chains, joined in a fixed order
+                        int d = 0;
+                        for (; d + 3 < width; d += 4) {
+                            d0 = fmaf(qrow[d], kr[d], d0);
+                            d1 = fmaf(qrow[d + 1], kr[d + 1], d1);
+                            d2 = fmaf(qrow[d + 2], kr[d + 2], d2);
+                            d3 = fmaf(qrow[d + 3], kr[d + 3], d3);
+                        }
+                        for (; d < width; ++d) d0 = fmaf(qrow[d], kr[d], d0);
+                        s[c] = ((d0 + d1) + (d2 + d3)) * p.scale;
                     }
                 }
                 tmax = fmaxf(tmax, s[c]);
@@ -203,7 +222,17 @@ latent_attention_partial_kernel(LatentParams p) {
             psum = warp_sum(psum);
             __syncwarp();
             float* ar = acc_s + (size_t)r * rank;
-            for (int d = lane; d < rank; d += 32) {
+            int d = lane;
+            for (; d + 96 < rank; d += 128) {                      // four features of a lane at a time
+                float a0 = ar[d] * corr, a1 = ar[d + 32] * corr, a2 = ar[d + 64] * corr, a3 = ar[d + 96] * corr;
+                for (int jj = 0; jj < tile; ++jj) {
+                    const float pj = pw[jj];
+                    const float* kr = k_s + jj * kstride + d;
+                    a0 = fmaf(pj, kr[0], a0); a1 = fmaf(pj, kr[32], a1); a2 = fmaf(pj, kr[64], a2); a3 = fmaf(pj, kr[96], a3);
+                }
+                ar[d] = a0; ar[d + 32] = a1; ar[d + 64] = a2; ar[d + 96] = a3;
+            }
+            for (; d < rank; d += 32) {
                 float a = ar[d] * corr;
                 for (int jj = 0; jj < tile; ++jj) a = fmaf(pw[jj], k_s[jj * kstride + d], a);
                 ar[d] = a;
@@ -250,6 +279,67 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, 
         for (int s = 0; s <= s_hi; ++s) acc = fmaf(part_o[(prow + s) * rank + d], expf(part_ml[(prow + s) * 2] - m), acc);
         o[d] = from_float<TO>(acc * inv);
     }
+}
+
+
+// ---------------------------------------------------------------------------------------------------------------
+// The other way round, for long prompt portions in bfloat16: make every head's keys and values of the request's
+// positions once per step (one product of the cached latents with [W_uk; W_uv]) and hand them, laid out as pages
+// of 64 positions of a pool of the step's own, to the grouped-query kernel on the tensor cores.  Per key and
+// head that costs dim + vdim features instead of rank + rot, and the products run at matrix speed.  Three
+// small kernels: the request's cached rows gathered into a matrix, the per-head rows put into pages (keys with the
+// shared rotated part behind them), and the rotation of the queries' rot part in place.
+
+// out[s, :] = the cached row of position s of request `req`, zeros where the block table holds no page.
+__global__ void latent_gather_kernel(const __nv_bfloat16* __restrict__ pool, const int* __restrict__ block_table, int max_pages,
+                                     int req, int num_pages, int page_size, int width, int S, __nv_bfloat16* __restrict__ out) {
+    pdl_launch();
+    pdl_wait();
+    const int s = blockIdx.x;
+    if (s >= S) return;
+    const int page = block_table[(size_t)req * max_pages + s / page_size];
+    const bool ok = page >= 0 && page < num_pages;
+    const __nv_bfloat16* src = pool + ((size_t)(ok ? page : 0) * page_size + s % page_size) * width;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) out[(size_t)s * width + d] = ok ? src[d] : __float2bfloat16_rn(0.0f);
+}
+
+// kv[s] = [k_plain (H x dim) | v (H x hd)] and rows[s] = [latent (rank) | rotated key part (rot)], hd = dim + rot:
+// pages[s / 64][0][h][s % 64] = [k_plain_h | key part], pages[s / 64][1][h][s % 64] = v_h.
+__global__ void latent_expand_kernel(const __nv_bfloat16* __restrict__ kv, int kv_stride, const __nv_bfloat16* __restrict__ rows,
+                                     int width, int rank, int H, int dim, int rot, int S, __nv_bfloat16* __restrict__ pages) {
+    pdl_launch();
+    pdl_wait();
+    const int s = blockIdx.x, h = blockIdx.y;
+    if (s >= S) return;
+    const int hd = dim + rot;
+    const size_t page_elems = (size_t)2 * H * 64 * hd;
+    __nv_bfloat16* kdst = pages + (size_t)(s / 64) * page_elems + ((size_t)h * 64 + s % 64) * hd;
+    __nv_bfloat16* vdst = kdst + (size_t)H * 64 * hd;
+    const __nv_bfloat16* kp = kv + (size_t)s * kv_stride + (size_t)h * dim;
+    const __nv_bfloat16* vp = kv + (size_t)s * kv_stride + (size_t)H * dim + (size_t)h * hd;
+    const __nv_bfloat16* kr = rows + (size_t)s * width + rank;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        kdst[d] = d < dim ? kp[d] : kr[d - dim];
+        vdst[d] = vp[d];
+    }
+}
+
+// q[t, h, off + 2i], q[t, h, off + 2i + 1] turn by cos_sin[t, i] for i < rot_dims / 2, in place.
+__global__ void rotate_q_kernel(__nv_bfloat16* __restrict__ q, int q_stride, int head, int off, int rot_dims, int H,
+                                const float* __restrict__ cos_sin, int T) {
+    pdl_launch();
+    pdl_wait();
+    const int half = rot_dims / 2;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)T * H * half) return;
+    const int k = (int)(i % half);
+    const int h = (int)((i / half) % H);
+    const int t = (int)(i / ((size_t)half * H));
+    __nv_bfloat16* p = q + (size_t)t * q_stride + (size_t)h * head + off + 2 * k;
+    const float u = __bfloat162float(p[0]), v = __bfloat162float(p[1]);
+    const float c = cos_sin[((size_t)t * half + k) * 2], sn = cos_sin[((size_t)t * half + k) * 2 + 1];
+    p[0] = __float2bfloat16_rn(u * c - v * sn);
+    p[1] = __float2bfloat16_rn(v * c + u * sn);
 }
 
 }  // namespace bg
@@ -337,6 +427,36 @@ extern "C" int bg_latent_attention_merge(const float* part_o, const float* part_
     BG_DISPATCH_DTYPE(out_dtype, TO,
         launch(latent_attention_merge_kernel<TO>, dim3(blocks), dim3(256), 0, stream, part_o, part_ml, positions, (TO*)out,
                out_head, out_row, T, H, rank, max_splits, split));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_latent_gather(const void* pool, const int* block_table, int max_pages, int req, int num_pages, int page_size,
+                                int width, int S, void* out, cudaStream_t stream) {
+    if (S <= 0) return BG_OK;
+    launch(latent_gather_kernel, dim3(S), dim3(128), 0, stream, (const __nv_bfloat16*)pool, block_table, max_pages, req, num_pages,
+           page_size, width, S, (__nv_bfloat16*)out);
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_latent_expand(const void* kv, int kv_stride, const void* rows, int width, int rank, int H, int dim, int rot,
+                                int S, void* pages, cudaStream_t stream) {
+    if (S <= 0) return BG_OK;
+    if (H <= 0 || H > 65535 || width != rank + rot) return BG_ERR_SHAPE;
+    launch(latent_expand_kernel, dim3(S, H), dim3(64), 0, stream, (const __nv_bfloat16*)kv, kv_stride, (const __nv_bfloat16*)rows,
+           width, rank, H, dim, rot, S, (__nv_bfloat16*)pages);
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_rotate_q(void* q, int q_stride, int head, int off, int rot_dims, int H, const float* cos_sin, int T,
+                           cudaStream_t stream) {
+    const long long n = (long long)T * H * (rot_dims / 2);
+    if (n <= 0) return BG_OK;
+    if (rot_dims & 1) return BG_ERR_SHAPE;
+    launch(rotate_q_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (__nv_bfloat16*)q, q_stride, head, off, rot_dims,
+           H, cos_sin, T);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

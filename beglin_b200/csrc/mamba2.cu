@@ -63,34 +63,38 @@ __global__ void conv_state_kernel(const TI* __restrict__ src, int src_stride, in
     }
 }
 
-// The scan.  One CTA per (head, request); thread (p, ns) = tid / NS, tid % NS owns S[n][p] for n = ns, ns + NS, ...
-// (NPT of them, in registers).  Per token:
+// The scan.  One CTA per (head, request, tile of PT columns p); thread (pl, ns) = tid / NS, tid % NS owns S[n][p0 + pl]
+// for n = ns, ns + NS, ... (NPT of them, in registers).  Per token:
 //   dt = softplus(dt_raw + dt_bias);  S = e^(-e^(A_log) dt) S + dt B x^T;  y = S^T C + D x.
 // The tokens go through shared memory in chunks of SCAN_CHUNK; the sum over n ends with shuffles among the NS
 // neighbouring lanes of a p.  A token's arithmetic does not depend on where the step was cut.
 constexpr int SCAN_CHUNK = 16;
+constexpr int SCAN_THREADS = 512;
 
 template <typename TI, typename TW, int NPT>
-__global__ void ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restrict__ src, int src_stride,
-                                int dt_col, const TW* __restrict__ dt_bias, const TW* __restrict__ A_log,
-                                const TW* __restrict__ Dw, float* __restrict__ state, size_t slot_stride,
-                                const int* __restrict__ slots, const int* __restrict__ reqs, float* __restrict__ y,
-                                int H, int P, int N, int G, int NS) {
+__global__ void __launch_bounds__(SCAN_THREADS)
+ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restrict__ src, int src_stride,
+                int dt_col, const TW* __restrict__ dt_bias, const TW* __restrict__ A_log,
+                const TW* __restrict__ Dw, float* __restrict__ state, size_t slot_stride,
+                const int* __restrict__ slots, const int* __restrict__ reqs, float* __restrict__ y,
+                int H, int P, int N, int G, int NS, int PT) {
     extern __shared__ float sm[];
     float* B_s = sm;                              // [CHUNK][N]
     float* C_s = B_s + SCAN_CHUNK * N;            // [CHUNK][N]
-    float* x_s = C_s + SCAN_CHUNK * N;            // [CHUNK][P]
-    float* y_s = x_s + SCAN_CHUNK * P;            // [CHUNK][P]
-    float* dt_s = y_s + SCAN_CHUNK * P;           // [CHUNK]
+    float* x_s = C_s + SCAN_CHUNK * N;            // [CHUNK][PT]
+    float* y_s = x_s + SCAN_CHUNK * PT;           // [CHUNK][PT]
+    float* dt_s = y_s + SCAN_CHUNK * PT;          // [CHUNK]
     float* da_s = dt_s + SCAN_CHUNK;              // [CHUNK]
     pdl_launch();
     pdl_wait();
-    const int h = blockIdx.x, req = blockIdx.y;
+    const int h = blockIdx.x, req = blockIdx.y, p0 = blockIdx.z * PT;
     const int row0 = reqs[req * 3 + 1], n = reqs[req * 3 + 2];
     if (n <= 0) return;
     const int tid = threadIdx.x;
-    const int pcol = tid / NS, ns = tid - pcol * NS;
-    const bool live = pcol < P;
+    const int pl = tid / NS, ns = tid - pl * NS;
+    const int pcol = p0 + pl;
+    const int pt = min(PT, P - p0);               // columns of this tile
+    const bool live = pl < pt;
     const int g = h / (H / G);
     const int inner = H * P;
     float* st = state + (size_t)slots[req] * slot_stride + (size_t)h * N * P;
@@ -114,9 +118,9 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int channels, con
             B_s[tt * N + nn] = Bsrc[row + nn];
             C_s[tt * N + nn] = Csrc[row + nn];
         }
-        for (int idx = tid; idx < tc * P; idx += blockDim.x) {
-            const int tt = idx / P, pp = idx - tt * P;
-            x_s[tt * P + pp] = xbc[(size_t)(row0 + c0 + tt) * channels + (size_t)h * P + pp];
+        for (int idx = tid; idx < tc * pt; idx += blockDim.x) {
+            const int tt = idx / pt, pp = idx - tt * pt;
+            x_s[tt * PT + pp] = xbc[(size_t)(row0 + c0 + tt) * channels + (size_t)h * P + p0 + pp];
         }
         if (tid < tc) {
             const float dt = softplus32(to_float(src[(size_t)(row0 + c0 + tid) * src_stride + dt_col + h]) + bias);
@@ -126,7 +130,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int channels, con
         __syncthreads();
         for (int tt = 0; tt < tc; ++tt) {
             const float dt = dt_s[tt], dA = da_s[tt];
-            const float xv = live ? x_s[tt * P + pcol] : 0.0f;
+            const float xv = live ? x_s[tt * PT + pl] : 0.0f;
             const float dtx = dt * xv;
             const float* Bt = B_s + tt * N;
             const float* Ct = C_s + tt * N;
@@ -140,12 +144,12 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int channels, con
                 }
             }
             for (int off = NS >> 1; off > 0; off >>= 1) yv += __shfl_xor_sync(0xffffffffu, yv, off);
-            if (live && ns == 0) y_s[tt * P + pcol] = fmaf(Dh, xv, yv);
+            if (live && ns == 0) y_s[tt * PT + pl] = fmaf(Dh, xv, yv);
         }
         __syncthreads();
-        for (int idx = tid; idx < tc * P; idx += blockDim.x) {
-            const int tt = idx / P, pp = idx - tt * P;
-            y[(size_t)(row0 + c0 + tt) * inner + (size_t)h * P + pp] = y_s[tt * P + pp];
+        for (int idx = tid; idx < tc * pt; idx += blockDim.x) {
+            const int tt = idx / pt, pp = idx - tt * pt;
+            y[(size_t)(row0 + c0 + tt) * inner + (size_t)h * P + p0 + pp] = y_s[tt * PT + pp];
         }
     }
 #pragma unroll
@@ -207,16 +211,16 @@ extern "C" int bg_conv_silu(const void* src, int src_dtype, int src_stride, int 
     return BG_OK;
 }
 
-// How the scan lays a head's state over a CTA: NS lanes share a column p (a power of two up to 32, with
-// P * NS threads at most 1024), each holding ceil(N / NS) values.  Returns 0, or BG_ERR_UNSUPPORTED.
-static int scan_layout(int P, int N, int* ns_out, int* npt_out) {
-    if (P <= 0 || N <= 0 || P > 1024) return BG_ERR_UNSUPPORTED;
+// How the scan lays a head's state over CTAs: tiles of PT columns p (at most 64), NS lanes per column (a power of
+// two up to 32 with PT * NS threads at most 512), each lane holding ceil(N / NS) values, at most 64.
+static int scan_layout(int P, int N, int* pt_out, int* ns_out, int* npt_out) {
+    if (P <= 0 || N <= 0) return BG_ERR_UNSUPPORTED;
+    const int pt = P < 64 ? P : 64;
     int ns = 1;
-    while (ns < 32 && P * ns * 2 <= 512 && ns * 2 <= N) ns *= 2;
-    while (ns < 32 && (N + ns - 1) / ns > 64 && P * ns * 2 <= 1024) ns *= 2;
+    while (ns < 32 && pt * ns * 2 <= SCAN_THREADS && ns * 2 <= N) ns *= 2;
     const int npt = (N + ns - 1) / ns;
     if (npt > 64) return BG_ERR_UNSUPPORTED;
-    *ns_out = ns; *npt_out = npt;
+    *pt_out = pt; *ns_out = ns; *npt_out = npt;
     return BG_OK;
 }
 
@@ -226,18 +230,20 @@ extern "C" int bg_ssm_scan(const float* xbc, int channels, const void* src, int 
                            int N, int G, cudaStream_t stream) {
     if (n_req <= 0) return BG_OK;
     if (H <= 0 || G <= 0 || H % G != 0 || n_req > 65535) return BG_ERR_SHAPE;
-    int ns = 0, npt = 0;
-    if (scan_layout(P, N, &ns, &npt) != BG_OK) return BG_ERR_UNSUPPORTED;
-    const int threads = (P * ns + 31) / 32 * 32;
-    const size_t smem = (size_t)(SCAN_CHUNK * (2 * N + 2 * P + 2)) * sizeof(float);
+    int pt = 0, ns = 0, npt = 0;
+    if (scan_layout(P, N, &pt, &ns, &npt) != BG_OK) return BG_ERR_UNSUPPORTED;
+    const int threads = (pt * ns + 31) / 32 * 32;
+    const int ptiles = (P + pt - 1) / pt;
+    if (ptiles > 65535) return BG_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)(SCAN_CHUNK * (2 * N + 2 * pt + 2)) * sizeof(float);
     if (smem > 200 * 1024) return BG_ERR_UNSUPPORTED;
-    dim3 grid(H, n_req);
+    dim3 grid(H, n_req, ptiles);
 #define BG_SCAN(NPT)                                                                                                  \
     do {                                                                                                              \
         auto kern = ssm_scan_kernel<TI, TW, NPT>;                                                                     \
         if (smem > BG_SMEM_OPT_IN) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         launch(kern, grid, dim3(threads), smem, stream, xbc, channels, (const TI*)src, src_stride, dt_col,            \
-               (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, state, (size_t)slot_stride, slots, reqs, y, H, P, N, G, ns); \
+               (const TW*)dt_bias, (const TW*)A_log, (const TW*)D, state, (size_t)slot_stride, slots, reqs, y, H, P, N, G, ns, pt); \
     } while (0)
     BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(w_dtype, TW, {
         if (npt <= 1) BG_SCAN(1);

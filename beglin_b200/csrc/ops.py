@@ -75,6 +75,9 @@ _SIGNATURES = {
                                     _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     "bg_latent_attention_merge": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int,
                                   _c_int, _c_int, _c_void_p],
+    "bg_latent_gather": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "bg_latent_expand": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "bg_rotate_q": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p],
     "bg_conv_silu": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_ll,
                      _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p],
     "bg_ssm_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
@@ -974,6 +977,50 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, dim: int, rot: in
                                              split, tile, bq, float(scale), _p(status), _stream()), "latent_attention_partial")
         _check(L.bg_latent_attention_merge(_p(part_o), _p(part_ml), _p(positions), _p(out), _dt(out), out.stride(0),
                                            out.stride(1), T, H, rank, n_splits, split, _stream()), "latent_attention_merge")
+
+
+def latent_gather(pool: torch.Tensor, block_table: torch.Tensor, req: int, S: int, out: torch.Tensor) -> None:
+    """out[s] = the cached row of position s < S of the step's request `req` (zeros where it holds no page); pool
+    [pages, page_size, width] and out [S, width], bfloat16."""
+    _cuda(pool, block_table, out)
+    _i32(block_table, "block_table")
+    if pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or pool.dim() != 3 or not pool.is_contiguous() \
+            or tuple(out.shape) != (S, pool.shape[2]) or not out.is_contiguous() or not 0 <= req < block_table.shape[0]:
+        raise KernelError("latent_gather: a bfloat16 pool [pages, page, width] and out [S, width]")
+    with phase("kv_expand"):
+        _check(lib().bg_latent_gather(_p(pool), _p(block_table), block_table.shape[1], req, pool.shape[0], pool.shape[1],
+                                      pool.shape[2], S, _p(out), _stream()), "latent_gather")
+
+
+def latent_expand(kv: torch.Tensor, rows: torch.Tensor, rank: int, H: int, dim: int, rot: int, pages: torch.Tensor) -> None:
+    """Per-head keys and values of S positions laid out as pages of 64 positions for the grouped-query kernels:
+    kv [S, H dim + H (dim + rot)] = [plain key parts | values], rows [S, rank + rot] (the rotated key part behind
+    the latent); pages [ceil(S / 64), 2, H, 64, dim + rot] receives keys [plain | rotated part] and values."""
+    _cuda(kv, rows, pages)
+    S, hd = kv.shape[0], dim + rot
+    for t in (kv, rows, pages):
+        if t.dtype != torch.bfloat16:
+            raise KernelError("latent_expand takes bfloat16 tensors")
+    if kv.stride(1) != 1 or kv.shape[1] != H * dim + H * hd or tuple(rows.shape) != (S, rank + rot) or not rows.is_contiguous():
+        raise KernelError(f"latent_expand: kv is {tuple(kv.shape)}, rows {tuple(rows.shape)}")
+    if tuple(pages.shape) != (-(-S // 64), 2, H, 64, hd) or not pages.is_contiguous():
+        raise KernelError(f"latent_expand: pages are {tuple(pages.shape)}")
+    with phase("kv_expand"):
+        _check(lib().bg_latent_expand(_p(kv), kv.stride(0), _p(rows), rank + rot, rank, H, dim, rot, S, _p(pages), _stream()),
+               "latent_expand")
+
+
+def rotate_q(q: torch.Tensor, H: int, head: int, off: int, rot_dims: int, cos_sin: torch.Tensor) -> None:
+    """In place: of every head (of `head` features) of the rows of q, features off + 2i and off + 2i + 1 turn by
+    cos_sin [T, rot_dims / 2, 2]."""
+    _cuda(q, cos_sin)
+    T = q.shape[0]
+    if q.dtype != torch.bfloat16 or q.stride(1) != 1 or q.shape[1] < H * head or off + rot_dims > head:
+        raise KernelError("rotate_q: bfloat16 rows of H heads")
+    if cos_sin.dtype != torch.float32 or cos_sin.shape[0] < T or cos_sin.shape[1] != rot_dims // 2 or not cos_sin.is_contiguous():
+        raise KernelError("rotate_q: cos_sin must be float32 [T, rot_dims/2, 2]")
+    with phase("rope"):
+        _check(lib().bg_rotate_q(_p(q), q.stride(0), head, off, rot_dims, H, _p(cos_sin), T, _stream()), "rotate_q")
 
 
 # ------------------------------------------------------------------------------------------------

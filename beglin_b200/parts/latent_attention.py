@@ -13,6 +13,12 @@ the gates (the matrices are concatenated at load time); norm of the query latent
 of the key/value latent; the query product; queries into the latent space; attention; values out of the
 latent space; gates; the output product.  A mixer with `own_kv` False has no key/value projection and reads
 the cache of the stage it is told to.
+
+Long prompt portions in bfloat16 go the other way round where the sizes allow it (dim + rot_dim = vdim = 64 or
+128): the keys and values of all heads are made once per step from the request's cached rows, by ONE product
+with [W_uk; W_uv], laid out as pages of a pool of the step's own, and the grouped-query kernel on the tensor
+cores (tcgen05) runs over them with one kv head per query head.  Per key and head that is dim + rot_dim + vdim
+features instead of 2 kv_rank + rot_dim, at matrix speed; the cache keeps holding the latent rows only.
 """
 from __future__ import annotations
 
@@ -80,6 +86,17 @@ class LatentAttention:
         self.hc = min(H, rows)                      # heads per CTA
         self.bq = max(1, rows // self.hc)           # rows of one request per CTA
         self.f32 = ctx.compute_dtype == torch.float32
+        # the tensor-core way for long portions: head sizes that the grouped-query kernel takes, bfloat16 throughout
+        self.expand = None
+        hd = spec.dim + spec.rot_dim
+        if not self.f32 and ctx.cache_dtype == torch.bfloat16 and spec.vdim == hd and hd in (64, 128) \
+                and ctx.attention in ("auto", "tcgen05"):
+            kernel, bq, tile = ops.attention_plan(1, hd, torch.bfloat16, False, ctx.attention, 64)
+            if kernel == "tc_rows":
+                self.expand = (bq, tile)
+                self.kv_up = ctx.matrix(torch.cat([tensors["k_up.weight"], tensors["v_up.weight"]], dim=0))
+
+    EXPAND_ROWS = 128          # portions of one request of at least this many rows make per-head keys and values
 
     def _per_head(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """out[h] = x[h] @ w[h]^T for x [H, T, K] (a view of any strides) and w [H, N, K]: [H, T, N]."""
@@ -93,6 +110,32 @@ class LatentAttention:
                 return torch.bmm(x, w.transpose(1, 2))
             return torch.bmm(x, w.transpose(1, 2), out_dtype=out_dtype)
 
+    def _per_head_keys(self, q: torch.Tensor, down: torch.Tensor, cos_sin, batch, cache: PagedKVView) -> torch.Tensor:
+        """The gated heads [T, H vdim] of a portion of ONE request, through keys and values made per head."""
+        s, ctx = self.spec, self.ctx
+        T, H, hd = batch.n_rows, s.n_heads, s.dim + s.rot_dim
+        S = batch.max_position + 1                                      # every position the portion's rows may see
+        rows = torch.empty((S, s.kv_rank + s.rot_dim), dtype=torch.bfloat16, device=q.device)
+        ops.latent_gather(cache.pool, cache.block_table, 0, S, rows)
+        with ops.phase("kv_expand"):
+            kv = torch.mm(rows[:, :s.kv_rank], self.kv_up.t())          # [S, H dim | H vdim]
+        pages = torch.empty((-(-S // 64), 2, H, 64, hd), dtype=torch.bfloat16, device=q.device)
+        pages[-1].zero_()                                               # what lies behind position S - 1 in the last page
+        ops.latent_expand(kv, rows, s.kv_rank, H, s.dim, s.rot_dim, pages)
+        if self.rot_dims:
+            ops.rotate_q(q, H, hd, s.dim, self.rot_dims, cos_sin)
+        table = torch.arange(pages.shape[0], dtype=torch.int32, device=q.device).view(1, -1)
+        bq, tile = self.expand
+        qblk, n_qblk = batch.query_blocks(bq)
+        att = torch.empty((T, H * hd), dtype=torch.bfloat16, device=q.device)
+        ops.attention(q, q.stride(0), pages, table, batch.positions, qblk, n_qblk, batch.max_position, T, H, H, hd, 0,
+                      ctx.kv_split, tile, bq, self.scale, att, ctx.status, "tc_rows")
+        if not s.gated:
+            return att
+        out = torch.empty((T, H * hd), dtype=torch.bfloat16, device=q.device)
+        ops.gate_heads(att.view(T, H, hd).transpose(0, 1), down, self.gate_col, out)
+        return out
+
     def forward(self, h: torch.Tensor, batch, cache: PagedKVView) -> torch.Tensor:
         s, ctx = self.spec, self.ctx
         T, H = batch.n_rows, s.n_heads
@@ -104,6 +147,8 @@ class LatentAttention:
         cq = torch.empty((T, s.q_rank), dtype=ctx.compute_dtype, device=h.device)
         ops.rmsnorm_slice(down, 0, s.q_rank, self.q_norm, s.eps, cq)
         q = self.q_up(cq)                                               # [T, H (dim + rot)]
+        if self.expand is not None and batch.n_req == 1 and T >= self.EXPAND_ROWS:
+            return self.o_proj.partial(self._per_head_keys(q, down, cos_sin, batch, cache))
         q_plain = q.view(T, H, s.dim + s.rot_dim)[:, :, :s.dim].transpose(0, 1)          # [H, T, dim]
         q_lat = self._per_head(q_plain, self.k_up_t, torch.float32)    # [H, T, kv_rank] float
         qblk, n_qblk = batch.query_blocks(self.bq)

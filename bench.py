@@ -338,6 +338,97 @@ def generate_point(cfg, requests=32, new_tokens=256, context=8192, seed=11):
     return out
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# The Sukisun decoder beside the Qwen2 decoder at equal layer sizes (--design sukisun): layer patterns and sizes
+# in the manner of real models of that kind (attention through a latent with a shared rotated key part, every
+# other attention layer reading its neighbour's cache, Mamba-2 layers of twice the width between them, a dense
+# feed-forward of four times the width), random weights.  The Qwen2 model beside it has the same width, number
+# of layers, heads and vocabulary, and a SwiGLU feed-forward with the same number of weights (three matrices of
+# 2/3 the inner size).
+def sukisun_config(width, heads, layers, vocab=32768):
+    lat = lambda kv_from=None: dict({"heads": heads, "dim": 64, "rot_dim": 64, "vdim": 128, "q_rank": width // 2,
+                                     "kv_rank": width // 4 if width <= 2048 else 512, "scale": 128 ** -0.5,
+                                     "rot": {"base": 10000.0, "dims": 64}}, **({} if kv_from is None else {"kv_from": kv_from}))
+    mam = {"heads": 2 * width // 128, "vdim": 128, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+    ff = {"kind": "dense", "ff": 4 * width}
+    out = []
+    for i in range(layers):
+        k = i % 4
+        if k == 2:
+            out.append({"type": "mamba2", "mixer": mam, "mlp": None})
+        else:
+            out.append({"type": "latent_attention", "mixer": lat(i - 1 if k == 1 else None), "mlp": ff})
+    return {"architecture": "Sukisun", "vocab": vocab, "width": width, "embedding": {"scale": float(width) ** 0.5},
+            "norm": {"eps": 1e-5}, "layers": out}
+
+
+def qwen2_like(width, heads, layers, vocab=32768):
+    return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": layers, "hidden_size": width,
+            "num_attention_heads": heads, "num_key_value_heads": max(1, heads // 4 if heads % 4 == 0 and heads > 12 else heads // 6), "intermediate_size": (8 * width // 3) // 128 * 128,
+            "vocab_size": vocab, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+            "use_sliding_window": False, "hidden_act": "silu", "max_position_embeddings": 32768}
+
+
+DESIGN_SIZES = {"1536": (1536, 12, 8), "4096": (4096, 32, 4)}      # width -> (width, heads, layers)
+
+
+def phase_times(eng, fn):
+    """Device milliseconds per kernel class of one call of fn (kernel by kernel, CUDA events around every class)."""
+    import torch
+    from beglin_b200.csrc import ops
+    graphs, eng.use_graphs = eng.use_graphs, False
+    fn()                                   # warm
+    torch.cuda.synchronize()
+    ops.profile_begin()
+    fn()
+    rec = ops.profile_end()
+    eng.use_graphs = graphs
+    return {k: round(ms, 4) for k, (ms, _) in rec.items()}
+
+
+def design_point(cfg, pk, batch, context, steps, warmup, tokens):
+    """Decoding (replayed graph) and one prompt step of `tokens` tokens for one configuration, with the device time per
+    kernel class of the prompt step and of one decoding step run kernel by kernel."""
+    import torch
+    from beglin_b200 import Engine
+    page = 64
+    eng = Engine.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=batch * (context + page), page_size=page,
+                        max_requests=batch, max_context=context + page)
+    out = {"weight_gb": round(eng.model.weight_bytes() / 1e9, 3), "cache_bytes_per_token": eng.cache.device_bytes() // max(1, eng.cache.num_pages + 1) // page}
+    pms = time_prefill(eng, tokens, reps=3, seed=3)
+    out["prefill_tok_s"] = round(tokens * 1000.0 / pms, 1)
+    out["prefill_ms"] = round(pms, 3)
+    g = torch.Generator().manual_seed(9)
+    ids = torch.randint(0, eng.vocab, (tokens,), generator=g).tolist()
+    out["prefill_classes_ms"] = phase_times(eng, lambda: eng.step([("p", ids, [tokens - 1])], end=["p"], check=False))
+    ms, launches, _ = time_decode(eng, batch, context, steps, warmup, seed=1, e2e=False)
+    out["decode_tok_s"] = round(batch * 1000.0 / ms, 1)
+    out["decode_ms"] = round(ms, 4)
+    out["decode_launches_per_step"] = launches // max(1, steps)
+    step_bytes = eng.model.weight_bytes() + batch * (context - steps / 2.0) * out["cache_bytes_per_token"]
+    out["decode_frac_of_hbm"] = round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+    rids = [("cls", i) for i in range(batch)]
+    fill_cache(eng, rids, context - 8, seed=4)
+    toks = [1] * batch
+    out["decode_classes_ms"] = phase_times(eng, lambda: eng.step([(r, [t], [0]) for r, t in zip(rids, toks)], check=False))
+    free_engine(eng)
+    return out
+
+
+def design_comparison(args, pk):
+    clocks = ClockSampler()
+    clocks.start()
+    rows = {}
+    for name in args.design_sizes.split(","):
+        width, heads, layers = DESIGN_SIZES[name]
+        for label, cfg in (("sukisun", sukisun_config(width, heads, layers)), ("qwen2", qwen2_like(width, heads, layers))):
+            rows[f"{label}_{name}"] = design_point(cfg, pk, args.batch, args.context, min(args.steps, 32), args.warmup, 2048)
+    print(json.dumps({"design": "sukisun beside qwen2 at equal layer sizes", "dtype": "bf16", "batch": args.batch,
+                      "context": args.context, "data": "synthetic (seeded uniform token ids, random weights)",
+                      "peaks": pk, "clocks": clocks.stop(), "points": rows}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -355,6 +446,10 @@ def main():
     ap.add_argument("--timeline", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                     help="instead of the measurement: print the kernels of one decode step (or of one prompt step of "
                          "2,048 tokens) with their device times")
+    ap.add_argument("--design", default=None, choices=["sukisun"],
+                    help="instead of the headline measurement: this design beside Qwen2 at equal layer sizes, prefill and "
+                         "decode, with the device time per kernel class")
+    ap.add_argument("--design-sizes", default="1536,4096", help="widths to compare at, of " + ",".join(sorted(DESIGN_SIZES)))
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -373,6 +468,8 @@ def main():
     import torch
     from beglin_b200 import Engine
     pk = peaks()
+    if args.design:
+        return design_comparison(args, pk)
     model_name, full = SIZES[args.sizes]
     args.layers = args.layers or full["num_hidden_layers"]
     cfg = dict(full, num_hidden_layers=args.layers)

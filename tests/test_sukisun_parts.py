@@ -187,7 +187,8 @@ def test_latent_attention_own_and_borrowed_cache(dtype, tol, dims):
 
 @pytest.mark.parametrize("dtype,tol", TOLS)
 @pytest.mark.parametrize("heads,vdim,state,groups,conv,norm_groups", [(4, 12, 20, 2, 3, 2), (2, 24, 9, 1, 2, 3),
-                                                                       (6, 8, 70, 3, 5, 1), (1, 40, 4, 1, 1, 5)])
+                                                                       (6, 8, 70, 3, 5, 1), (1, 40, 4, 1, 1, 5),
+                                                                       (2, 80, 16, 2, 4, 1)])
 def test_mamba2_portions_and_two_requests(dtype, tol, heads, vdim, state, groups, conv, norm_groups):
     """Two sequences through one mixer in steps that hold portions of both (17 and 1, 1 and 30, 3 and 2, ...), against
     the plain recurrence over each whole sequence; then a third request in the slot that the first gave back."""
@@ -244,3 +245,35 @@ def test_mamba2_state_is_kept_in_32_bit():
     assert need.dtype == "float32" and need.shape == (2 * 3 * 4 + 3 * (8 + 6),)
     reqs = Requests([need], 8, torch.bfloat16)
     assert reqs.cache.state_groups[0].slab.dtype == torch.float32
+
+
+@pytest.mark.parametrize("dim,rot,dims", [(32, 32, 32), (48, 16, 8), (64, 64, 64)])
+def test_latent_attention_long_portions_through_per_head_keys(dim, rot, dims):
+    """bfloat16 with dim + rot_dim = vdim = 64 or 128: a portion of one request of 128 rows and more makes every head's
+    keys and values from the cached rows and runs the grouped-query kernel on the tensor cores; shorter portions and
+    single tokens score against the cached rows themselves.  Both against the plain function, the second portion
+    seeing what the first left in the cache."""
+    from beglin_b200.parts import LatentAttentionSpec, PositionSpec
+    from beglin_b200.parts.latent_attention import LatentAttention
+    dtype = torch.bfloat16
+    ctx = ctx_for(dtype, page=16, kv_split=64)
+    d, eps, T = 96, 1e-5, 391
+    pos = PositionSpec(kind="rope", rotary_dim=dims, theta=1000.0, pairing="interleaved")
+    spec = LatentAttentionSpec(hidden=d, n_heads=3, dim=dim, rot_dim=rot, vdim=dim + rot, q_rank=40, kv_rank=56, scale=0.2,
+                               eps=eps, position=pos)
+    t = latent_weights(spec, 500, dtype)
+    part = LatentAttention(spec, t, ctx)
+    assert part.expand is not None
+    h = rnd(T, d, seed=8).to(dtype)
+    reqs = Requests([LatentAttention.cache_need(spec)], 16, dtype)
+    outs, at = [], 0
+    for n in (150, 40, 200, 1):                        # per-head keys, cached rows, per-head keys over 190 earlier positions, one token
+        b = reqs.batch([("r", n)])
+        o = part.forward(h[at:at + n].to(DEV), b, reqs.cache.view(0, b))
+        outs.append(o.float().sum(0) if o.dim() == 3 else o.float())
+        at += n
+    m = {"heads": 3, "dim": dim, "rot_dim": rot, "vdim": dim + rot, "kv_rank": 56, "scale": 0.2, "rot": {"base": 1000.0, "dims": dims}}
+    w = plain_names(t, "a.")
+    c, kr = plain.latent_of(h.double(), w, "a.", m, eps)
+    want = plain.latent_attention(h.double(), w, "a.", m, eps, c, kr)
+    assert rel_err(torch.cat(outs), want) < 3e-2
