@@ -75,6 +75,11 @@ _SIGNATURES = {
                                     _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     "bg_latent_attention_merge": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int,
                                   _c_int, _c_int, _c_void_p],
+    "bg_latent_attention_mma_plan": [_c_int, _c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
+    "bg_latent_attention_mma_partial": [_c_void_p, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
+                                        _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
+                                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                        _c_void_p, _c_void_p],
     "bg_latent_gather": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "bg_latent_expand": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "bg_rotate_q": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p],
@@ -919,6 +924,15 @@ def latent_attention_plan(rank: int, rot: int) -> Tuple[int, int]:
     return rows.value, tile.value
 
 
+def latent_attention_mma_plan(rank: int, rot: int) -> Optional[Tuple[int, int]]:
+    """(rows per CTA, stages) of the tensor-core latent attention kernel, or None when it does not take a cache row of
+    rank + rot features (a multiple of 32, rank a multiple of 8 up to 512)."""
+    rows, stages = _c_int(0), _c_int(0)
+    if lib().bg_latent_attention_mma_plan(rank, rot, ctypes.byref(rows), ctypes.byref(stages)) != 0:
+        return None
+    return rows.value, stages.value
+
+
 def latent_append(src: torch.Tensor, col0: int, rank: int, rot: int, rot_dims: int, weight: torch.Tensor, eps: float,
                   cos_sin: Optional[torch.Tensor], positions: torch.Tensor, row_req: torch.Tensor,
                   block_table: torch.Tensor, pool: torch.Tensor, status: Optional[torch.Tensor]) -> None:
@@ -948,11 +962,14 @@ def latent_append(src: torch.Tensor, col0: int, rank: int, rot: int, rot_dims: i
 def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, dim: int, rot: int, rot_dims: int,
                      cos_sin: Optional[torch.Tensor], pool: torch.Tensor, block_table: torch.Tensor,
                      positions: torch.Tensor, qblk: torch.Tensor, n_qblk: int, max_position: int, bq: int, hc: int,
-                     tile: int, split: int, scale: float, out: torch.Tensor, status: Optional[torch.Tensor]) -> None:
+                     tile: int, split: int, scale: float, out: torch.Tensor, status: Optional[torch.Tensor],
+                     mma_stages: int = 0) -> None:
     """Causal attention of a step's rows over the latent cache.  q_lat float32 [H, T, rank]: the queries carried into
     the latent space; q_raw [T, H * (dim + rot)]: the query product's rows, whose rot part is rotated here; pool
     [pages, page_size, rank + rot]; out [H, T, rank] receives, per head, the softmax-weighted sum of the cached
-    latents.  `qblk` is cut for `bq` rows; a CTA takes `hc` heads; keys are cut into splits of `split` positions."""
+    latents.  `qblk` is cut for `bq` rows; a CTA takes `hc` heads; keys are cut into splits of `split` positions.
+    With `mma_stages` 1 or 2 the products run on the tensor cores (bfloat16 q_raw and pool, bq * hc at most 64, sizes as
+    `latent_attention_mma_plan` says); else on the CUDA cores in float, for every size and type."""
     _cuda(q_lat, q_raw, cos_sin, pool, block_table, positions, qblk, out, status)
     _i32(positions, "positions"); _i32(block_table, "block_table"); _i32(qblk, "qblk")
     H, T, rank = q_lat.shape
@@ -970,11 +987,21 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, dim: int, rot: in
     part_ml = torch.empty((T * H * n_splits, 2), dtype=torch.float32, device=q_lat.device)
     L = lib()
     with phase("attn"):
-        _check(L.bg_latent_attention_partial(_p(q_lat), _dt(q_lat), q_lat.stride(0), q_lat.stride(1), _p(q_raw), _dt(q_raw),
-                                             q_raw.stride(0), dim + rot, dim, _p(cos_sin), _p(pool), _dt(pool), pool.shape[0],
-                                             pool.shape[1], _p(block_table), block_table.shape[1], _p(positions), _p(qblk),
-                                             n_qblk, _p(part_o), _p(part_ml), n_splits, n_splits, H, hc, rank, rot, rot_dims,
-                                             split, tile, bq, float(scale), _p(status), _stream()), "latent_attention_partial")
+        if mma_stages:
+            if q_raw.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16:
+                raise KernelError("latent_attention: the tensor-core kernel takes bfloat16 query rows and caches")
+            _check(L.bg_latent_attention_mma_partial(_p(q_lat), q_lat.stride(0), q_lat.stride(1), _p(q_raw), q_raw.stride(0),
+                                                     dim + rot, dim, _p(cos_sin), _p(pool), pool.shape[0], pool.shape[1],
+                                                     _p(block_table), block_table.shape[1], _p(positions), _p(qblk), n_qblk,
+                                                     _p(part_o), _p(part_ml), n_splits, n_splits, H, hc, rank, rot, rot_dims,
+                                                     split, bq, mma_stages, float(scale), _p(status), _stream()),
+                   "latent_attention_mma_partial")
+        else:
+            _check(L.bg_latent_attention_partial(_p(q_lat), _dt(q_lat), q_lat.stride(0), q_lat.stride(1), _p(q_raw), _dt(q_raw),
+                                                 q_raw.stride(0), dim + rot, dim, _p(cos_sin), _p(pool), _dt(pool), pool.shape[0],
+                                                 pool.shape[1], _p(block_table), block_table.shape[1], _p(positions), _p(qblk),
+                                                 n_qblk, _p(part_o), _p(part_ml), n_splits, n_splits, H, hc, rank, rot, rot_dims,
+                                                 split, tile, bq, float(scale), _p(status), _stream()), "latent_attention_partial")
         _check(L.bg_latent_attention_merge(_p(part_o), _p(part_ml), _p(positions), _p(out), _dt(out), out.stride(0),
                                            out.stride(1), T, H, rank, n_splits, split, _stream()), "latent_attention_merge")
 

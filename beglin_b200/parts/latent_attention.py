@@ -86,6 +86,15 @@ class LatentAttention:
         self.hc = min(H, rows)                      # heads per CTA
         self.bq = max(1, rows // self.hc)           # rows of one request per CTA
         self.f32 = ctx.compute_dtype == torch.float32
+        # bfloat16 steps score on the tensor cores where the cached row's sizes allow it (mma.sync); float32 steps and
+        # other sizes on the CUDA cores
+        self.mma = None
+        if not self.f32 and ctx.cache_dtype == torch.bfloat16 and ctx.attention != "generic":
+            plan = ops.latent_attention_mma_plan(spec.kv_rank, spec.rot_dim)
+            if plan is not None:
+                rows, stages = plan
+                hc = min(H, rows)
+                self.mma = (hc, max(1, rows // hc), stages)
         # the tensor-core way for long portions: head sizes that the grouped-query kernel takes, bfloat16 throughout
         self.expand = None
         hd = spec.dim + spec.rot_dim
@@ -151,14 +160,17 @@ class LatentAttention:
             return self.o_proj.partial(self._per_head_keys(q, down, cos_sin, batch, cache))
         q_plain = q.view(T, H, s.dim + s.rot_dim)[:, :, :s.dim].transpose(0, 1)          # [H, T, dim]
         q_lat = self._per_head(q_plain, self.k_up_t, torch.float32)    # [H, T, kv_rank] float
-        qblk, n_qblk = batch.query_blocks(self.bq)
+        hc, bq, stages = (self.hc, self.bq, 0) if self.mma is None else self.mma
+        if getattr(batch, "decode_only", False):
+            bq = 1                                                      # one row per request: a CTA's rows are its heads
+        qblk, n_qblk = batch.query_blocks(bq)
         if qblk is None:                                                # a decoding graph's batch keeps its list implicit
             batch.implicit_blocks = False
-            qblk, n_qblk = batch.query_blocks(self.bq)
+            qblk, n_qblk = batch.query_blocks(bq)
         o_lat = torch.empty((H, T, s.kv_rank), dtype=ctx.compute_dtype, device=h.device)
         ops.latent_attention(q_lat, q, s.dim, s.rot_dim, self.rot_dims, cos_sin, cache.pool, cache.block_table,
-                             batch.positions, qblk, n_qblk, batch.max_position, self.bq, self.hc, self.tile, ctx.kv_split,
-                             self.scale, o_lat, ctx.status)
+                             batch.positions, qblk, n_qblk, batch.max_position, bq, hc, self.tile, ctx.kv_split,
+                             self.scale, o_lat, ctx.status, mma_stages=stages)
         v = self._per_head(o_lat, self.v_up, ctx.compute_dtype)        # [H, T, vdim]
         out = torch.empty((T, H * s.vdim), dtype=ctx.compute_dtype, device=h.device)
         if s.gated:

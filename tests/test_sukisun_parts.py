@@ -277,3 +277,72 @@ def test_latent_attention_long_portions_through_per_head_keys(dim, rot, dims):
     c, kr = plain.latent_of(h.double(), w, "a.", m, eps)
     want = plain.latent_attention(h.double(), w, "a.", m, eps, c, kr)
     assert rel_err(torch.cat(outs), want) < 3e-2
+
+
+@pytest.mark.parametrize("H,rank,rot,dims", [(6, 96, 32, 32), (3, 64, 64, 16), (20, 256, 64, 64), (40, 512, 64, 64), (1, 24, 8, 8)])
+def test_latent_attention_kernels_agree(H, rank, rot, dims):
+    """The tensor-core kernel (bfloat16 products, float sums) against the CUDA-core kernel (float throughout) on the same
+    bfloat16 cache: three requests of 5, 333 and 70 positions whose steps bring 5, 40 and 1 rows, over pages of 16 and
+    splits of 64 keys; then the three with one row each, the way a decoding step runs.  And the CUDA-core kernel against
+    a plain softmax over the cached rows."""
+    from beglin_b200.csrc import ops
+    from beglin_b200.parts import PagedLatentNeed
+    plan = ops.latent_attention_mma_plan(rank, rot)
+    assert plan is not None
+    rows_mma, stages = plan
+    width, dim = rank + rot, 8
+    reqs = Requests([PagedLatentNeed(width)], 16, torch.bfloat16, pages=40)
+    lens = {"a": 5, "b": 333, "c": 70}
+    new = {"a": 5, "b": 40, "c": 1}
+    for r, n in lens.items():                              # what the requests hold before the step
+        if n > new[r]:
+            reqs.batch([(r, n - new[r])])
+    pool = reqs.cache.kv_groups[0].device_pool[0]
+    pool.copy_(rnd(*pool.shape, seed=1, scale=0.5).to(torch.bfloat16))
+    for decode in (False, True):
+        portions = [(r, 1 if decode else new[r]) for r in lens]
+        b = reqs.batch(portions)
+        T = b.n_rows
+        view = reqs.cache.view(0, b)
+        q_lat = rnd(H, T, rank, seed=2, scale=0.3).to(DEV)
+        q_raw = rnd(T, H * (dim + rot), seed=3).to(torch.bfloat16).to(DEV)
+        cos_sin = None
+        if dims:
+            ang = rnd(T, dims // 2, seed=4)
+            cos_sin = torch.stack([torch.cos(ang), torch.sin(ang)], -1).contiguous().to(DEV)
+        outs = {}
+        for name in ("generic", "mma"):
+            if name == "generic":
+                rows, tile = ops.latent_attention_plan(rank, rot)
+                hc, st = min(H, rows), 0
+            else:
+                rows, tile, st = rows_mma, 64, stages
+                hc = min(H, rows)
+            bq = 1 if decode else max(1, rows // hc)
+            qblk, n_qblk = b.query_blocks(bq)
+            out = torch.empty((H, T, rank), dtype=torch.float32, device=DEV)
+            ops.latent_attention(q_lat, q_raw, dim, rot, dims, cos_sin, view.pool, view.block_table, b.positions, qblk, n_qblk,
+                                 b.max_position, bq, hc, tile, 64, 0.2, out, None, mma_stages=st)
+            outs[name] = out.cpu().double()
+        assert torch.isfinite(outs["mma"]).all()
+        assert rel_err(outs["mma"], outs["generic"]) < 2e-2, decode
+        # the plain softmax over the cached rows, for every row of the step
+        qr = q_raw.float().cpu().double().reshape(T, H, dim + rot)[:, :, dim:]
+        if dims:
+            cs = cos_sin.cpu().double()
+            u, v = qr[..., 0:dims:2].clone(), qr[..., 1:dims:2].clone()
+            qr = qr.clone()
+            qr[..., 0:dims:2] = u * cs[:, None, :, 0] - v * cs[:, None, :, 1]
+            qr[..., 1:dims:2] = v * cs[:, None, :, 0] + u * cs[:, None, :, 1]
+        row = 0
+        for i, (r, n) in enumerate(portions):
+            table = view.block_table[i].cpu()
+            for k in range(n):
+                pos = int(b.positions[row])
+                keys = torch.stack([pool[int(table[s // 16]), s % 16] for s in range(pos + 1)]).float().cpu().double()
+                for hh in range(H):
+                    qfull = torch.cat([q_lat[hh, row].cpu().double(), qr[row, hh]])
+                    pr = torch.softmax(keys @ qfull * 0.2, 0)
+                    want = pr @ keys[:, :rank]
+                    assert (outs["generic"][hh, row] - want).abs().max() < 1e-4 * max(1.0, float(want.abs().max())), (r, k, hh)
+                row += 1
