@@ -99,28 +99,31 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     const int g = lane >> 2, t4 = lane & 3;
     const int n_rows = nq * nh;                                    // row r = (query r / nh, head h0 + r % nh)
     const int half = p.rot_dims / 2;
-    for (int idx = tid; idx < ROWS * width; idx += LM_THREADS) {
-        const int r = idx / width, d = idx - r * width;
-        float v = 0.0f;
-        if (r < n_rows) {
-            const int qi = r / nh, hh = r - qi * nh;
-            const int t = row0 + qi, h = h0 + hh;
-            if (d < rank) {
-                v = p.q_lat[(size_t)h * p.ql_head + (size_t)t * p.ql_row + d];
-            } else {
-                const int e = d - rank;
-                const __nv_bfloat16* src = p.q_raw + (size_t)t * p.qr_row + (size_t)h * p.qr_head + p.qr_off;
-                if (e < p.rot_dims) {
-                    const int i = e >> 1;
-                    const float u = __bfloat162float(src[2 * i]), w = __bfloat162float(src[2 * i + 1]);
-                    const float c = p.cos_sin[((size_t)t * half + i) * 2], sn = p.cos_sin[((size_t)t * half + i) * 2 + 1];
-                    v = (e & 1) ? (w * c + u * sn) : (u * c - w * sn);
-                } else {
-                    v = __bfloat162float(src[e]);
-                }
-            }
+    // the rows' queries as bfloat16: a warp per row, the latent part with four loads of a lane on their way at a time
+    for (int r = warp; r < ROWS; r += LM_WARPS) {
+        __nv_bfloat16* qd = q_s + (size_t)r * ks_stride;
+        if (r >= n_rows) {
+            for (int d = lane; d < width; d += 32) qd[d] = __float2bfloat16_rn(0.0f);
+            continue;
         }
-        q_s[(size_t)r * ks_stride + d] = __float2bfloat16_rn(v);
+        const int qi = r / nh, hh = r - qi * nh;
+        const int t = row0 + qi, h = h0 + hh;
+        const float* ql = p.q_lat + (size_t)h * p.ql_head + (size_t)t * p.ql_row;
+        int d = lane;
+        for (; d + 96 < rank; d += 128) {
+            const float a0 = ql[d], a1 = ql[d + 32], a2 = ql[d + 64], a3 = ql[d + 96];
+            qd[d] = __float2bfloat16_rn(a0); qd[d + 32] = __float2bfloat16_rn(a1);
+            qd[d + 64] = __float2bfloat16_rn(a2); qd[d + 96] = __float2bfloat16_rn(a3);
+        }
+        for (; d < rank; d += 32) qd[d] = __float2bfloat16_rn(ql[d]);
+        const __nv_bfloat16* src = p.q_raw + (size_t)t * p.qr_row + (size_t)h * p.qr_head + p.qr_off;
+        for (int i = lane; i < half; i += 32) {
+            const float u = __bfloat162float(src[2 * i]), w = __bfloat162float(src[2 * i + 1]);
+            const float c = p.cos_sin[((size_t)t * half + i) * 2], sn = p.cos_sin[((size_t)t * half + i) * 2 + 1];
+            qd[rank + 2 * i] = __float2bfloat16_rn(u * c - w * sn);
+            qd[rank + 2 * i + 1] = __float2bfloat16_rn(w * c + u * sn);
+        }
+        for (int e = p.rot_dims + lane; e < p.rot; e += 32) qd[rank + e] = src[e];
     }
     for (int r = tid; r < ROWS; r += LM_THREADS) {
         m_s[r] = -INFINITY; l_s[r] = 0.0f; corr_s[r] = 1.0f;
@@ -143,25 +146,26 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     auto fetch = [&](int ti, int st) {
         const int t0 = k_begin + ti * LM_TILE;
         __nv_bfloat16* kd = k_s + (size_t)st * LM_TILE * ks_stride;
-        for (int idx = tid; idx < LM_TILE * chunks; idx += LM_THREADS) {
-            const int j = idx / chunks, c = idx - j * chunks;
-            const int key = t0 + j;
-            bool ok = false;
-            const __nv_bfloat16* src = nullptr;
-            if (key < k_end) {
-                const int page = p.block_table[(size_t)req * p.max_pages + key / p.page_size];
-                if (page < 0 || page >= p.num_pages) {
-                    if (p.status && c == 0) atomicOr(p.status, BG_STATUS_BAD_PAGE);
-                } else {
-                    ok = true;
-                    src = p.pool + ((size_t)page * p.page_size + key % p.page_size) * width + c * 8;
-                }
+        const int j = tid >> 2, c0 = tid & 3;                      // four threads share a key's row
+        const int key = t0 + j;
+        bool ok = false;
+        const __nv_bfloat16* src = nullptr;
+        if (key < k_end) {
+            const int page = p.block_table[(size_t)req * p.max_pages + key / p.page_size];
+            if (page < 0 || page >= p.num_pages) {
+                if (p.status && c0 == 0) atomicOr(p.status, BG_STATUS_BAD_PAGE);
+            } else {
+                ok = true;
+                src = p.pool + ((size_t)page * p.page_size + key % p.page_size) * width;
             }
-            __nv_bfloat16* dst = kd + (size_t)j * ks_stride + c * 8;
-            if (ok) lm_cp_async16(dst, src);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
-            if (c == 0) ok_s[st * LM_TILE + j] = ok ? 1 : 0;
         }
+        __nv_bfloat16* dst = kd + (size_t)j * ks_stride;
+        if (ok) {
+            for (int c = c0; c < chunks; c += 4) lm_cp_async16(dst + c * 8, src + c * 8);
+        } else {
+            for (int c = c0; c < chunks; c += 4) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (c0 == 0) ok_s[st * LM_TILE + j] = ok ? 1 : 0;
         lm_cp_async_commit();
     };
 
@@ -332,7 +336,7 @@ extern "C" int bg_latent_attention_mma_partial(const float* q_lat, long long ql_
     const int width = rank + rot;
     if (H <= 0 || hc <= 0 || hc > H || width % 32 != 0 || rank % 8 != 0 || rank > 512 || rot_dims > rot || (rot_dims & 1))
         return BG_ERR_SHAPE;
-    if (split % LM_TILE != 0 || bq <= 0 || bq * hc > 64 || (stages != 1 && stages != 2)) return BG_ERR_SHAPE;
+    if (split % LM_TILE != 0 || bq <= 0 || bq * hc > 64) return BG_ERR_SHAPE;
     const int chunks = (H + hc - 1) / hc;
     if (n_splits_launch > max_splits || n_splits_launch > 65535 || chunks > 65535) return BG_ERR_SHAPE;
     const int rows = bq * hc <= 16 ? 16 : (bq * hc <= 32 ? 32 : 64);
@@ -343,6 +347,14 @@ extern "C" int bg_latent_attention_mma_partial(const float* q_lat, long long ql_
     p.page_size = page_size; p.block_table = block_table; p.max_pages = max_pages; p.positions = positions; p.qblk = qblk;
     p.part_o = part_o; p.part_ml = part_ml; p.max_splits = max_splits; p.H = H; p.hc = hc; p.rank = rank; p.rot = rot;
     p.rot_dims = rot_dims; p.split = split; p.bq = bq; p.stages = stages; p.scale = scale; p.status = status;
+    // stages: two CTAs on an SM overlap one another's loads, queries and epilogues, so a CTA takes no more than half
+    // of an SM's shared memory where it can (with two tiles in flight if they fit that, else with one); a CTA too
+    // large for that is alone on its SM and takes two tiles if they fit
+    (void)stages;
+    const size_t half_sm = 110 * 1024, whole_sm = 200 * 1024;
+    const size_t s1 = latent_mma_smem(rows, width, 1), s2 = latent_mma_smem(rows, width, 2);
+    stages = s2 <= half_sm ? 2 : (s1 <= half_sm ? 1 : (s2 <= whole_sm ? 2 : 1));
+    p.stages = stages;
     const size_t smem = latent_mma_smem(rows, width, stages);
     if (smem > 227 * 1024) return BG_ERR_UNSUPPORTED;
     dim3 grid(n_qblk, chunks, n_splits_launch);

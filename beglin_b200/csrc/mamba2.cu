@@ -63,8 +63,10 @@ __global__ void conv_state_kernel(const TI* __restrict__ src, int src_stride, in
     }
 }
 
-// The scan.  One CTA per (head, request, tile of PT columns p); thread (pl, ns) = tid / NS, tid % NS owns S[n][p0 + pl]
-// for n = ns, ns + NS, ... (NPT of them, in registers).  Per token:
+// The scan.  One CTA per (head, request, tile of PT columns p); thread (pl, ns) = tid / NS, tid % NS owns NPT values
+// S[n][p0 + pl] in registers: for NPT >= 4 the n come in runs of four, n = ((k / 4) NS + ns) 4 + k % 4, so that a
+// token's B and C reach a thread as 16-byte loads from shared memory without bank conflicts between the NS
+// neighbours (B and C are padded with zeros up to NPT NS values); for fewer, n = ns + k NS.  Per token:
 //   dt = softplus(dt_raw + dt_bias);  S = e^(-e^(A_log) dt) S + dt B x^T;  y = S^T C + D x.
 // The tokens go through shared memory in chunks of SCAN_CHUNK; the sum over n ends with shuffles among the NS
 // neighbouring lanes of a p.  A token's arithmetic does not depend on where the step was cut.
@@ -79,9 +81,10 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restric
                 const int* __restrict__ slots, const int* __restrict__ reqs, float* __restrict__ y,
                 int H, int P, int N, int G, int NS, int PT) {
     extern __shared__ float sm[];
-    float* B_s = sm;                              // [CHUNK][N]
-    float* C_s = B_s + SCAN_CHUNK * N;            // [CHUNK][N]
-    float* x_s = C_s + SCAN_CHUNK * N;            // [CHUNK][PT]
+    const int NP = NPT * NS;                      // N rounded up to what the threads hold
+    float* B_s = sm;                              // [CHUNK][NP]
+    float* C_s = B_s + SCAN_CHUNK * NP;           // [CHUNK][NP]
+    float* x_s = C_s + SCAN_CHUNK * NP;           // [CHUNK][PT]
     float* y_s = x_s + SCAN_CHUNK * PT;           // [CHUNK][PT]
     float* dt_s = y_s + SCAN_CHUNK * PT;          // [CHUNK]
     float* da_s = dt_s + SCAN_CHUNK;              // [CHUNK]
@@ -98,10 +101,11 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restric
     const int g = h / (H / G);
     const int inner = H * P;
     float* st = state + (size_t)slots[req] * slot_stride + (size_t)h * N * P;
+    constexpr bool RUNS = NPT >= 4;               // runs of four n per thread
     float S[NPT];
 #pragma unroll
     for (int k = 0; k < NPT; ++k) {
-        const int nn = ns + k * NS;
+        const int nn = RUNS ? ((k >> 2) * NS + ns) * 4 + (k & 3) : ns + k * NS;
         S[k] = (live && nn < N) ? st[(size_t)nn * P + pcol] : 0.0f;
     }
     const float a = expf(to_float(A_log[h]));
@@ -112,11 +116,11 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restric
     for (int c0 = 0; c0 < n; c0 += SCAN_CHUNK) {
         const int tc = min(SCAN_CHUNK, n - c0);
         __syncthreads();
-        for (int idx = tid; idx < tc * N; idx += blockDim.x) {
-            const int tt = idx / N, nn = idx - tt * N;
+        for (int idx = tid; idx < tc * NP; idx += blockDim.x) {
+            const int tt = idx / NP, nn = idx - tt * NP;
             const size_t row = (size_t)(row0 + c0 + tt) * channels;
-            B_s[tt * N + nn] = Bsrc[row + nn];
-            C_s[tt * N + nn] = Csrc[row + nn];
+            B_s[idx] = nn < N ? Bsrc[row + nn] : 0.0f;
+            C_s[idx] = nn < N ? Csrc[row + nn] : 0.0f;
         }
         for (int idx = tid; idx < tc * pt; idx += blockDim.x) {
             const int tt = idx / pt, pp = idx - tt * pt;
@@ -132,13 +136,26 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restric
             const float dt = dt_s[tt], dA = da_s[tt];
             const float xv = live ? x_s[tt * PT + pl] : 0.0f;
             const float dtx = dt * xv;
-            const float* Bt = B_s + tt * N;
-            const float* Ct = C_s + tt * N;
+            const float* Bt = B_s + tt * NP;
+            const float* Ct = C_s + tt * NP;
             float yv = 0.0f;
+            if (RUNS) {                                        // padded n hold B = C = 0: their S stays 0
+                const float4* B4 = reinterpret_cast<const float4*>(Bt) + ns;
+                const float4* C4 = reinterpret_cast<const float4*>(Ct) + ns;
+                float y1 = 0.0f;
 #pragma unroll
-            for (int k = 0; k < NPT; ++k) {
-                const int nn = ns + k * NS;
-                if (nn < N) {
+                for (int kq = 0; kq < NPT / 4; ++kq) {
+                    const float4 b = B4[kq * NS], c = C4[kq * NS];
+                    S[4 * kq + 0] = fmaf(dA, S[4 * kq + 0], dtx * b.x); yv = fmaf(S[4 * kq + 0], c.x, yv);
+                    S[4 * kq + 1] = fmaf(dA, S[4 * kq + 1], dtx * b.y); y1 = fmaf(S[4 * kq + 1], c.y, y1);
+                    S[4 * kq + 2] = fmaf(dA, S[4 * kq + 2], dtx * b.z); yv = fmaf(S[4 * kq + 2], c.z, yv);
+                    S[4 * kq + 3] = fmaf(dA, S[4 * kq + 3], dtx * b.w); y1 = fmaf(S[4 * kq + 3], c.w, y1);
+                }
+                yv += y1;
+            } else {
+#pragma unroll
+                for (int k = 0; k < NPT; ++k) {
+                    const int nn = ns + k * NS;
                     S[k] = fmaf(dA, S[k], dtx * Bt[nn]);
                     yv = fmaf(S[k], Ct[nn], yv);
                 }
@@ -154,7 +171,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restric
     }
 #pragma unroll
     for (int k = 0; k < NPT; ++k) {
-        const int nn = ns + k * NS;
+        const int nn = RUNS ? ((k >> 2) * NS + ns) * 4 + (k & 3) : ns + k * NS;
         if (live && nn < N) st[(size_t)nn * P + pcol] = S[k];
     }
 }
@@ -235,7 +252,8 @@ extern "C" int bg_ssm_scan(const float* xbc, int channels, const void* src, int 
     const int threads = (pt * ns + 31) / 32 * 32;
     const int ptiles = (P + pt - 1) / pt;
     if (ptiles > 65535) return BG_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(SCAN_CHUNK * (2 * N + 2 * pt + 2)) * sizeof(float);
+    const int npt_t = npt <= 1 ? 1 : npt <= 2 ? 2 : npt <= 4 ? 4 : npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64;
+    const size_t smem = (size_t)(SCAN_CHUNK * (2 * npt_t * ns + 2 * pt + 2)) * sizeof(float);
     if (smem > 200 * 1024) return BG_ERR_UNSUPPORTED;
     dim3 grid(H, n_req, ptiles);
 #define BG_SCAN(NPT)                                                                                                  \
