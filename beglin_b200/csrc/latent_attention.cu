@@ -21,19 +21,34 @@ namespace bg {
 constexpr int LAT_THREADS = 256;
 constexpr int LAT_WARPS = LAT_THREADS / 32;
 
-// One row per step row: the RMS norm of the latent and the rotation of the shared key part, stored at the
+// One block per step row: the RMS norm of the latent and the rotation of the shared key part, stored at the
 // row's position in the pages.  src row = [.. | latent raw (rank) | key part raw (rot) | ..] from col0.
 // Pairs (2i, 2i+1) of the first rot_dims features of the key part turn by the row's angles; the rest pass.
-template <typename TI, typename TW, typename TC>
+// With q_out, the same block also norms the row's query latent src[q_col0 .. q_col0 + q_rank) into q_out[t]
+// (the two norms read the same product's row, so they share a launch).
+template <typename TI, typename TW, typename TC, typename TQ>
 __global__ void latent_append_kernel(const TI* __restrict__ src, int src_stride, int col0, int rank, int rot, int rot_dims,
                                      const TW* __restrict__ w, float eps, const float* __restrict__ cos_sin,
                                      const int* __restrict__ positions, const int* __restrict__ row_req,
                                      const int* __restrict__ block_table, int max_pages, TC* __restrict__ pool,
-                                     int num_pages, int page_size, unsigned* status) {
+                                     int num_pages, int page_size, unsigned* status, int q_col0, int q_rank,
+                                     const TW* __restrict__ q_w, TQ* __restrict__ q_out) {
     __shared__ float red[32];
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
+    if (q_out) {
+        const TI* qs = src + (size_t)t * src_stride + q_col0;
+        float qq = 0.0f;
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
+            const float v = to_float(qs[i]);
+            qq += v * v;
+        }
+        qq = block_sum(qq, red);
+        const float qinv = 1.0f / sqrtf(qq / (float)q_rank + eps);
+        TQ* qo = q_out + (size_t)t * q_rank;
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) qo[i] = from_float<TQ>(to_float(qs[i]) * qinv * to_float(q_w[i]));
+    }
     const TI* s = src + (size_t)t * src_stride + col0;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < rank; i += blockDim.x) {
@@ -368,13 +383,16 @@ extern "C" int bg_latent_attention_plan(int rank, int rot, int* rows_out, int* t
 extern "C" int bg_latent_append(const void* src, int src_dtype, int src_stride, int col0, int rank, int rot, int rot_dims,
                                 const void* w, int w_dtype, float eps, const float* cos_sin, const int* positions,
                                 const int* row_req, const int* block_table, int max_pages, void* pool, int pool_dtype,
-                                int num_pages, int page_size, int n_rows, unsigned* status, cudaStream_t stream) {
+                                int num_pages, int page_size, int n_rows, unsigned* status, int q_col0, int q_rank,
+                                const void* q_w, void* q_out, int q_dtype, cudaStream_t stream) {
     if (n_rows <= 0) return BG_OK;
     if (rank <= 0 || rot < 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1)) return BG_ERR_SHAPE;
-    BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(w_dtype, TW, BG_DISPATCH_DTYPE(pool_dtype, TC,
-        launch(latent_append_kernel<TI, TW, TC>, dim3(n_rows), dim3(128), 0, stream, (const TI*)src, src_stride, col0, rank,
+    if (q_out && q_rank <= 0) return BG_ERR_SHAPE;
+    if (!q_out) q_dtype = pool_dtype;
+    BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(w_dtype, TW, BG_DISPATCH_DTYPE(pool_dtype, TC, BG_DISPATCH_DTYPE(q_dtype, TQ,
+        launch(latent_append_kernel<TI, TW, TC, TQ>, dim3(n_rows), dim3(128), 0, stream, (const TI*)src, src_stride, col0, rank,
                rot, rot_dims, (const TW*)w, eps, cos_sin, positions, row_req, block_table, max_pages, (TC*)pool, num_pages,
-               page_size, status))));
+               page_size, status, q_col0, q_rank, (const TW*)q_w, (TQ*)q_out)))));
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

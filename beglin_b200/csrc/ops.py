@@ -68,7 +68,7 @@ _SIGNATURES = {
     "bg_latent_attention_plan": [_c_int, _c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
     "bg_latent_append": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_float, _c_void_p,
                          _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p,
-                         _c_void_p],
+                         _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p],
     "bg_latent_attention_partial": [_c_void_p, _c_int, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                                     _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
                                     _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -935,11 +935,13 @@ def latent_attention_mma_plan(rank: int, rot: int) -> Optional[Tuple[int, int]]:
 
 def latent_append(src: torch.Tensor, col0: int, rank: int, rot: int, rot_dims: int, weight: torch.Tensor, eps: float,
                   cos_sin: Optional[torch.Tensor], positions: torch.Tensor, row_req: torch.Tensor,
-                  block_table: torch.Tensor, pool: torch.Tensor, status: Optional[torch.Tensor]) -> None:
+                  block_table: torch.Tensor, pool: torch.Tensor, status: Optional[torch.Tensor],
+                  q_norm: Optional[tuple] = None) -> None:
     """For every row t of src: pool[page, slot] = [rmsnorm(src[t, col0 : col0+rank]) * weight |
     rotate(src[t, col0+rank : col0+rank+rot])] at positions[t] of request row_req[t]; pool is
     [pages, page_size, rank + rot].  The first rot_dims features of the key part turn in pairs (2i, 2i+1) by
-    cos_sin [T, rot_dims/2, 2]."""
+    cos_sin [T, rot_dims/2, 2].  With q_norm = (q_col0, q_weight, q_out) the same launch also writes
+    q_out[t] = rmsnorm(src[t, q_col0 : q_col0 + q_rank]) * q_weight, q_out [T, q_rank], the weights of one type."""
     _cuda(src, weight, cos_sin, positions, row_req, block_table, pool, status)
     _i32(positions, "positions"); _i32(row_req, "row_req"); _i32(block_table, "block_table")
     T = positions.numel()
@@ -952,11 +954,20 @@ def latent_append(src: torch.Tensor, col0: int, rank: int, rot: int, rot_dims: i
     if rot_dims > 0 and (cos_sin is None or cos_sin.dtype != torch.float32 or cos_sin.shape[0] < T
                          or cos_sin.shape[1] != rot_dims // 2 or not cos_sin.is_contiguous()):
         raise KernelError("latent_append: cos_sin must be float32 [T, rot_dims/2, 2]")
+    q_col0, q_rank, q_w, q_out = 0, 0, None, None
+    if q_norm is not None:
+        q_col0, q_w, q_out = q_norm
+        _cuda(q_w, q_out)
+        q_rank = q_w.numel()
+        if q_w.dtype != weight.dtype or not q_w.is_contiguous() or tuple(q_out.shape) != (T, q_rank) or not q_out.is_contiguous() \
+                or q_col0 < 0 or q_col0 + q_rank > src.shape[1]:
+            raise KernelError("latent_append: the query latent's norm wants q_out [T, q_rank] and a weight of the other's type")
     with phase("rope+kv_write"):
         _check(lib().bg_latent_append(_p(src), _dt(src), src.stride(0), col0, rank, rot, rot_dims, _p(weight), _dt(weight),
                                       float(eps), _p(cos_sin), _p(positions), _p(row_req), _p(block_table),
                                       block_table.shape[1], _p(pool), _dt(pool), pool.shape[0], pool.shape[1], T, _p(status),
-                                      _stream()), "latent_append")
+                                      q_col0, q_rank, _p(q_w), _p(q_out), _dt(q_out) if q_out is not None else F32, _stream()),
+               "latent_append")
 
 
 def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, dim: int, rot: int, rot_dims: int,

@@ -150,11 +150,13 @@ class LatentAttention:
         T, H = batch.n_rows, s.n_heads
         down = self.down(h, out_dtype=torch.float32)                    # [T, q_rank (+ kv_rank + rot) (+ H)]
         cos_sin = self.position.table(batch) if self.rot_dims else None
-        if s.own_kv:
-            ops.latent_append(down, self.kv_col, s.kv_rank, s.rot_dim, self.rot_dims, self.kv_norm, s.eps, cos_sin,
-                              batch.positions, batch.row_req, cache.block_table, cache.pool, ctx.status)
         cq = torch.empty((T, s.q_rank), dtype=ctx.compute_dtype, device=h.device)
-        ops.rmsnorm_slice(down, 0, s.q_rank, self.q_norm, s.eps, cq)
+        if s.own_kv:                                                    # both norms of the product's rows in one launch
+            ops.latent_append(down, self.kv_col, s.kv_rank, s.rot_dim, self.rot_dims, self.kv_norm, s.eps, cos_sin,
+                              batch.positions, batch.row_req, cache.block_table, cache.pool, ctx.status,
+                              q_norm=(0, self.q_norm, cq))
+        else:
+            ops.rmsnorm_slice(down, 0, s.q_rank, self.q_norm, s.eps, cq)
         q = self.q_up(cq)                                               # [T, H (dim + rot)]
         if self.expand is not None and batch.n_req == 1 and T >= self.EXPAND_ROWS:
             return self.o_proj.partial(self._per_head_keys(q, down, cos_sin, batch, cache))
