@@ -73,6 +73,61 @@ __global__ void conv_state_kernel(const TI* __restrict__ src, int src_stride, in
 constexpr int SCAN_CHUNK = 16;
 constexpr int SCAN_THREADS = 512;
 
+__device__ __forceinline__ void scan_cp_async4(float* smem_dst, const float* gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(gmem_src) : "memory");
+}
+
+
+// U tokens of the recurrence for one thread's states: the states move token by token, the U sums over n are then
+// brought together side by side (their shuffles in flight together), and the U results stored.
+template <int U, int NPT>
+__device__ __forceinline__ void scan_tokens(float (&S)[NPT], const float* __restrict__ B_s, const float* __restrict__ C_s,
+                                            const float* __restrict__ x_s, const float* __restrict__ dt_s,
+                                            const float* __restrict__ da_s, float* __restrict__ y_s, int tt, int NP, int PT,
+                                            int NS, int ns, int pl, bool live, float Dh) {
+    float yv[U], xv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const float dt = dt_s[tt + u], dA = da_s[tt + u];
+        xv[u] = live ? x_s[(tt + u) * PT + pl] : 0.0f;
+        const float dtx = dt * xv[u];
+        const float* Bt = B_s + (tt + u) * NP;
+        const float* Ct = C_s + (tt + u) * NP;
+        float y0 = 0.0f;
+        if (NPT >= 4) {                                        // padded n hold B = C = 0: their S stays 0
+            const float4* B4 = reinterpret_cast<const float4*>(Bt) + ns;
+            const float4* C4 = reinterpret_cast<const float4*>(Ct) + ns;
+            float y1 = 0.0f;
+#pragma unroll
+            for (int kq = 0; kq < NPT / 4; ++kq) {
+                const float4 b = B4[kq * NS], c = C4[kq * NS];
+                S[4 * kq + 0] = fmaf(dA, S[4 * kq + 0], dtx * b.x); y0 = fmaf(S[4 * kq + 0], c.x, y0);
+                S[4 * kq + 1] = fmaf(dA, S[4 * kq + 1], dtx * b.y); y1 = fmaf(S[4 * kq + 1], c.y, y1);
+                S[4 * kq + 2] = fmaf(dA, S[4 * kq + 2], dtx * b.z); y0 = fmaf(S[4 * kq + 2], c.z, y0);
+                S[4 * kq + 3] = fmaf(dA, S[4 * kq + 3], dtx * b.w); y1 = fmaf(S[4 * kq + 3], c.w, y1);
+            }
+            y0 += y1;
+        } else {
+#pragma unroll
+            for (int k = 0; k < NPT; ++k) {
+                const int nn = ns + k * NS;
+                S[k] = fmaf(dA, S[k], dtx * Bt[nn]);
+                y0 = fmaf(S[k], Ct[nn], y0);
+            }
+        }
+        yv[u] = y0;
+    }
+    for (int off = NS >> 1; off > 0; off >>= 1) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) yv[u] += __shfl_xor_sync(0xffffffffu, yv[u], off);
+    }
+    if (live && ns == 0) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) y_s[(tt + u) * PT + pl] = fmaf(Dh, xv[u], yv[u]);
+    }
+}
+
 template <typename TI, typename TW, int NPT>
 __global__ void __launch_bounds__(SCAN_THREADS)
 ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restrict__ src, int src_stride,
@@ -82,12 +137,9 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restric
                 int H, int P, int N, int G, int NS, int PT) {
     extern __shared__ float sm[];
     const int NP = NPT * NS;                      // N rounded up to what the threads hold
-    float* B_s = sm;                              // [CHUNK][NP]
-    float* C_s = B_s + SCAN_CHUNK * NP;           // [CHUNK][NP]
-    float* x_s = C_s + SCAN_CHUNK * NP;           // [CHUNK][PT]
-    float* y_s = x_s + SCAN_CHUNK * PT;           // [CHUNK][PT]
-    float* dt_s = y_s + SCAN_CHUNK * PT;          // [CHUNK]
-    float* da_s = dt_s + SCAN_CHUNK;              // [CHUNK]
+    // two buffers of [CHUNK][NP] B, [CHUNK][NP] C, [CHUNK][PT] x, [CHUNK] dt, [CHUNK] decay; one [CHUNK][PT] y
+    const int buf_floats = SCAN_CHUNK * (2 * NP + PT + 2);
+    float* y_s = sm + 2 * buf_floats;
     pdl_launch();
     pdl_wait();
     const int h = blockIdx.x, req = blockIdx.y, p0 = blockIdx.z * PT;
@@ -113,56 +165,63 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restric
     const float Dh = to_float(Dw[h]);
     const float* Bsrc = xbc + inner + (size_t)g * N;
     const float* Csrc = xbc + inner + (size_t)G * N + (size_t)g * N;
-    for (int c0 = 0; c0 < n; c0 += SCAN_CHUNK) {
+    const float* xsrc = xbc + (size_t)h * P + p0;
+    // the padding of B and C (n from N up to NP) is zero for good: it is written once, the copies never touch it
+    for (int idx = tid; idx < 2 * SCAN_CHUNK * (NP - N); idx += blockDim.x) {
+        const int bsel = idx / (SCAN_CHUNK * (NP - N)), r = idx - bsel * SCAN_CHUNK * (NP - N);
+        const int tt = r / (NP - N), nn = N + (r - tt * (NP - N));
+        float* bb = sm + bsel * buf_floats;
+        bb[tt * NP + nn] = 0.0f;
+        bb[SCAN_CHUNK * NP + tt * NP + nn] = 0.0f;
+    }
+    // a chunk's B, C and x on their way into a buffer: 4-byte asynchronous copies, so that they all are in flight at
+    // once and the chunk after the one being computed is under way meanwhile
+    auto issue = [&](int c0, int bsel) {
+        float* bb = sm + bsel * buf_floats;
         const int tc = min(SCAN_CHUNK, n - c0);
-        __syncthreads();
-        for (int idx = tid; idx < tc * NP; idx += blockDim.x) {
-            const int tt = idx / NP, nn = idx - tt * NP;
+        for (int tt = 0; tt < tc; ++tt) {
             const size_t row = (size_t)(row0 + c0 + tt) * channels;
-            B_s[idx] = nn < N ? Bsrc[row + nn] : 0.0f;
-            C_s[idx] = nn < N ? Csrc[row + nn] : 0.0f;
+            for (int nn = tid; nn < N; nn += blockDim.x) {
+                scan_cp_async4(bb + tt * NP + nn, Bsrc + row + nn);
+                scan_cp_async4(bb + SCAN_CHUNK * NP + tt * NP + nn, Csrc + row + nn);
+            }
+            for (int pp = tid; pp < pt; pp += blockDim.x) scan_cp_async4(bb + 2 * SCAN_CHUNK * NP + tt * PT + pp, xsrc + row + pp);
         }
-        for (int idx = tid; idx < tc * pt; idx += blockDim.x) {
-            const int tt = idx / pt, pp = idx - tt * pt;
-            x_s[tt * PT + pp] = xbc[(size_t)(row0 + c0 + tt) * channels + (size_t)h * P + p0 + pp];
-        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    auto raw_dt = [&](int c0) {
+        return (tid < min(SCAN_CHUNK, n - c0)) ? to_float(src[(size_t)(row0 + c0 + tid) * src_stride + dt_col + h]) : 0.0f;
+    };
+    issue(0, 0);
+    float dt_raw = raw_dt(0);
+    int bsel = 0;
+    for (int c0 = 0; c0 < n; c0 += SCAN_CHUNK, bsel ^= 1) {
+        const int tc = min(SCAN_CHUNK, n - c0);
+        float* bb = sm + bsel * buf_floats;
+        const float* B_s = bb;
+        const float* C_s = bb + SCAN_CHUNK * NP;
+        const float* x_s = bb + 2 * SCAN_CHUNK * NP;
+        float* dt_s = bb + 2 * SCAN_CHUNK * NP + SCAN_CHUNK * PT;
+        float* da_s = dt_s + SCAN_CHUNK;
         if (tid < tc) {
-            const float dt = softplus32(to_float(src[(size_t)(row0 + c0 + tid) * src_stride + dt_col + h]) + bias);
+            const float dt = softplus32(dt_raw + bias);
             dt_s[tid] = dt;
             da_s[tid] = expf(-a * dt);
         }
-        __syncthreads();
-        for (int tt = 0; tt < tc; ++tt) {
-            const float dt = dt_s[tt], dA = da_s[tt];
-            const float xv = live ? x_s[tt * PT + pl] : 0.0f;
-            const float dtx = dt * xv;
-            const float* Bt = B_s + tt * NP;
-            const float* Ct = C_s + tt * NP;
-            float yv = 0.0f;
-            if (RUNS) {                                        // padded n hold B = C = 0: their S stays 0
-                const float4* B4 = reinterpret_cast<const float4*>(Bt) + ns;
-                const float4* C4 = reinterpret_cast<const float4*>(Ct) + ns;
-                float y1 = 0.0f;
-#pragma unroll
-                for (int kq = 0; kq < NPT / 4; ++kq) {
-                    const float4 b = B4[kq * NS], c = C4[kq * NS];
-                    S[4 * kq + 0] = fmaf(dA, S[4 * kq + 0], dtx * b.x); yv = fmaf(S[4 * kq + 0], c.x, yv);
-                    S[4 * kq + 1] = fmaf(dA, S[4 * kq + 1], dtx * b.y); y1 = fmaf(S[4 * kq + 1], c.y, y1);
-                    S[4 * kq + 2] = fmaf(dA, S[4 * kq + 2], dtx * b.z); yv = fmaf(S[4 * kq + 2], c.z, yv);
-                    S[4 * kq + 3] = fmaf(dA, S[4 * kq + 3], dtx * b.w); y1 = fmaf(S[4 * kq + 3], c.w, y1);
-                }
-                yv += y1;
-            } else {
-#pragma unroll
-                for (int k = 0; k < NPT; ++k) {
-                    const int nn = ns + k * NS;
-                    S[k] = fmaf(dA, S[k], dtx * Bt[nn]);
-                    yv = fmaf(S[k], Ct[nn], yv);
-                }
-            }
-            for (int off = NS >> 1; off > 0; off >>= 1) yv += __shfl_xor_sync(0xffffffffu, yv, off);
-            if (live && ns == 0) y_s[tt * PT + pl] = fmaf(Dh, xv, yv);
+        const bool more = c0 + SCAN_CHUNK < n;
+        if (more) {
+            issue(c0 + SCAN_CHUNK, bsel ^ 1);
+            dt_raw = raw_dt(c0 + SCAN_CHUNK);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
+        __syncthreads();
+        int tt = 0;
+        for (; tt + 4 <= tc; tt += 4)
+            scan_tokens<4, NPT>(S, B_s, C_s, x_s, dt_s, da_s, y_s, tt, NP, PT, NS, ns, pl, live, Dh);
+        for (; tt < tc; ++tt)
+            scan_tokens<1, NPT>(S, B_s, C_s, x_s, dt_s, da_s, y_s, tt, NP, PT, NS, ns, pl, live, Dh);
         __syncthreads();
         for (int idx = tid; idx < tc * pt; idx += blockDim.x) {
             const int tt = idx / pt, pp = idx - tt * pt;
@@ -228,15 +287,24 @@ extern "C" int bg_conv_silu(const void* src, int src_dtype, int src_stride, int 
     return BG_OK;
 }
 
-// How the scan lays a head's state over CTAs: tiles of PT columns p (at most 64), NS lanes per column (a power of
-// two up to 32 with PT * NS threads at most 512), each lane holding ceil(N / NS) values, at most 64.
-static int scan_layout(int P, int N, int* pt_out, int* ns_out, int* npt_out) {
+// How the scan lays a head's state over CTAs: tiles of PT columns p, NS lanes per column (a power of two up to 32),
+// each lane holding ceil(N / NS) values.  The tokens of a request come one after the other, so the time of a prompt
+// is one CTA's time per token times the tokens.  What a token costs a thread besides its states (step size, input,
+// the shuffles, the loop) is paid per thread, which speaks for many states a thread; the chain of dependent
+// instructions of a token grows with them, which speaks for few: 8 states a thread set NS.  PT is the largest of
+// 64, 32, 16, 8 that gives ONE request a CTA for every SM (heads x tiles).  The choice depends on the model's sizes
+// alone, never on the step, so that a row's sums run in the same order in every step.
+static int scan_layout(int H, int P, int N, int* pt_out, int* ns_out, int* npt_out) {
     if (P <= 0 || N <= 0) return BG_ERR_UNSUPPORTED;
-    const int pt = P < 64 ? P : 64;
     int ns = 1;
-    while (ns < 32 && pt * ns * 2 <= SCAN_THREADS && ns * 2 <= N) ns *= 2;
+    while (ns < 32 && (N + ns - 1) / ns > 8) ns *= 2;
     const int npt = (N + ns - 1) / ns;
     if (npt > 64) return BG_ERR_UNSUPPORTED;
+    const int sms = sm_count();
+    int pt = 8;
+    for (int cand = 64; cand >= 8; cand >>= 1)
+        if (cand * ns <= SCAN_THREADS && (long long)H * ((P + cand - 1) / cand) >= sms) { pt = cand; break; }
+    if (pt > P) pt = P;
     *pt_out = pt; *ns_out = ns; *npt_out = npt;
     return BG_OK;
 }
@@ -248,12 +316,12 @@ extern "C" int bg_ssm_scan(const float* xbc, int channels, const void* src, int 
     if (n_req <= 0) return BG_OK;
     if (H <= 0 || G <= 0 || H % G != 0 || n_req > 65535) return BG_ERR_SHAPE;
     int pt = 0, ns = 0, npt = 0;
-    if (scan_layout(P, N, &pt, &ns, &npt) != BG_OK) return BG_ERR_UNSUPPORTED;
+    if (scan_layout(H, P, N, &pt, &ns, &npt) != BG_OK) return BG_ERR_UNSUPPORTED;
     const int threads = (pt * ns + 31) / 32 * 32;
     const int ptiles = (P + pt - 1) / pt;
     if (ptiles > 65535) return BG_ERR_UNSUPPORTED;
     const int npt_t = npt <= 1 ? 1 : npt <= 2 ? 2 : npt <= 4 ? 4 : npt <= 8 ? 8 : npt <= 16 ? 16 : npt <= 32 ? 32 : 64;
-    const size_t smem = (size_t)(SCAN_CHUNK * (2 * npt_t * ns + 2 * pt + 2)) * sizeof(float);
+    const size_t smem = (size_t)(SCAN_CHUNK * (2 * (2 * npt_t * ns + pt + 2) + pt)) * sizeof(float);
     if (smem > 200 * 1024) return BG_ERR_UNSUPPORTED;
     dim3 grid(H, n_req, ptiles);
 #define BG_SCAN(NPT)                                                                                                  \
