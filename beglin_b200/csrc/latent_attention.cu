@@ -269,33 +269,40 @@ latent_attention_partial_kernel(LatentParams p) {
 }
 
 // out[h][t][:] = sum_s o_s e^(m_s - m) / sum_s l_s e^(m_s - m) over the splits 0 .. position / split, in split
-// order.  One warp per (row, head).
+// order.  One block of 128 threads per (row, head): the splits' weights are worked out once, by the first warp, and
+// every thread then sums its features over the splits with all its loads independent of one another (a warp per
+// (row, head) that recomputed the weights for every 32 features took 32 us for 96 rows of 17 splits).
+constexpr int LAT_MERGE_THREADS = 128;
 template <typename TO>
-__global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                              const int* __restrict__ positions, TO* __restrict__ out, long long out_head,
-                                              int out_row, int T, int H, int rank, int max_splits, int split) {
+__global__ void __launch_bounds__(LAT_MERGE_THREADS)
+latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                              const int* __restrict__ positions, TO* __restrict__ out, long long out_head,
+                              int out_row, int T, int H, int rank, int max_splits, int split) {
+    extern __shared__ float f_s[];                 // [max_splits] weights e^(m_s - m) / l
     pdl_launch();
     pdl_wait();
-    const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (w >= T * H) return;
+    const int w = blockIdx.x;
     const int t = w / H, h = w - t * H;
     const int s_hi = positions[t] / split;
     const size_t prow = (size_t)w * max_splits;
-    float m = -INFINITY;
-    for (int s = lane; s <= s_hi; s += 32) m = fmaxf(m, part_ml[(prow + s) * 2]);
-    m = warp_max(m);
-    float l = 0.0f;
-    for (int s = 0; s <= s_hi; ++s) l = fmaf(part_ml[(prow + s) * 2 + 1], expf(part_ml[(prow + s) * 2] - m), l);
-    const float inv = 1.0f / l;
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x < 32) {
+        float m = -INFINITY;
+        for (int s = lane; s <= s_hi; s += 32) m = fmaxf(m, part_ml[(prow + s) * 2]);
+        m = warp_max(m);
+        float l = 0.0f;
+        for (int s = 0; s <= s_hi; ++s) l = fmaf(part_ml[(prow + s) * 2 + 1], expf(part_ml[(prow + s) * 2] - m), l);
+        const float inv = 1.0f / l;
+        for (int s = lane; s <= s_hi; s += 32) f_s[s] = expf(part_ml[(prow + s) * 2] - m) * inv;
+    }
+    __syncthreads();
     TO* o = out + (size_t)h * out_head + (size_t)t * out_row;
-    for (int d = lane; d < rank; d += 32) {
+    for (int d = threadIdx.x; d < rank; d += LAT_MERGE_THREADS) {
         float acc = 0.0f;
-        for (int s = 0; s <= s_hi; ++s) acc = fmaf(part_o[(prow + s) * rank + d], expf(part_ml[(prow + s) * 2] - m), acc);
-        o[d] = from_float<TO>(acc * inv);
+        for (int s = 0; s <= s_hi; ++s) acc = fmaf(part_o[(prow + s) * rank + d], f_s[s], acc);
+        o[d] = from_float<TO>(acc);
     }
 }
-
 
 // ---------------------------------------------------------------------------------------------------------------
 // The other way round, for long prompt portions in bfloat16: make every head's keys and values of the request's
@@ -305,38 +312,57 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, 
 // small kernels: the request's cached rows gathered into a matrix, the per-head rows put into pages (keys with the
 // shared rotated part behind them), and the rotation of the queries' rot part in place.
 
-// out[s, :] = the cached row of position s of request `req`, zeros where the block table holds no page.
+// lat[s, :] and kr[s, :] = the latent and the rotated key part of the cached row of position s of request `req`,
+// zeros where the block table holds no page.  Two matrices, so that the product that follows reads a dense one.
 __global__ void latent_gather_kernel(const __nv_bfloat16* __restrict__ pool, const int* __restrict__ block_table, int max_pages,
-                                     int req, int num_pages, int page_size, int width, int S, __nv_bfloat16* __restrict__ out) {
+                                     int req, int num_pages, int page_size, int rank, int rot, int S,
+                                     __nv_bfloat16* __restrict__ lat, __nv_bfloat16* __restrict__ kr) {
     pdl_launch();
     pdl_wait();
     const int s = blockIdx.x;
     if (s >= S) return;
+    const int width = rank + rot;
     const int page = block_table[(size_t)req * max_pages + s / page_size];
     const bool ok = page >= 0 && page < num_pages;
     const __nv_bfloat16* src = pool + ((size_t)(ok ? page : 0) * page_size + s % page_size) * width;
-    for (int d = threadIdx.x; d < width; d += blockDim.x) out[(size_t)s * width + d] = ok ? src[d] : __float2bfloat16_rn(0.0f);
+    const __nv_bfloat16 zero = __float2bfloat16_rn(0.0f);
+    if ((width & 7) == 0 && (rank & 7) == 0) {                 // rows and both parts on 16-byte boundaries
+        for (int c = threadIdx.x; c < width / 8; c += blockDim.x) {
+            const uint4 v = ok ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+            __nv_bfloat16* dst = c * 8 < rank ? lat + (size_t)s * rank + c * 8 : kr + (size_t)s * rot + (c * 8 - rank);
+            *reinterpret_cast<uint4*>(dst) = v;
+        }
+        return;
+    }
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        const __nv_bfloat16 v = ok ? src[d] : zero;
+        if (d < rank) lat[(size_t)s * rank + d] = v;
+        else kr[(size_t)s * rot + d - rank] = v;
+    }
 }
 
-// kv[s] = [k_plain (H x dim) | v (H x hd)] and rows[s] = [latent (rank) | rotated key part (rot)], hd = dim + rot:
-// pages[s / 64][0][h][s % 64] = [k_plain_h | key part], pages[s / 64][1][h][s % 64] = v_h.
-__global__ void latent_expand_kernel(const __nv_bfloat16* __restrict__ kv, int kv_stride, const __nv_bfloat16* __restrict__ rows,
-                                     int width, int rank, int H, int dim, int rot, int S, __nv_bfloat16* __restrict__ pages) {
+// kv[s] = [k_plain (H x dim) | v (H x hd)] and kr[s] = the rotated key part (rot), hd = dim + rot:
+// pages[s / 64][0][h][s % 64] = [k_plain_h | key part], pages[s / 64][1][h][s % 64] = v_h.  A thread moves 16 bytes
+// (dim and rot are multiples of 8 wherever the grouped-query kernel takes the head size).
+__global__ void latent_expand_kernel(const __nv_bfloat16* __restrict__ kv, int kv_stride, const __nv_bfloat16* __restrict__ kr,
+                                     int H, int dim, int rot, int S, __nv_bfloat16* __restrict__ pages) {
     pdl_launch();
     pdl_wait();
-    const int s = blockIdx.x, h = blockIdx.y;
-    if (s >= S) return;
-    const int hd = dim + rot;
+    const int hd = dim + rot, cpr = hd / 8;                    // 16-byte pieces per row
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t n = (size_t)S * H * 2 * cpr;
+    if (i >= n) return;
+    const int c = (int)(i % cpr);
+    const int kvsel = (int)((i / cpr) % 2);
+    const int h = (int)((i / ((size_t)cpr * 2)) % H);
+    const int s = (int)(i / ((size_t)cpr * 2 * H));
     const size_t page_elems = (size_t)2 * H * 64 * hd;
-    __nv_bfloat16* kdst = pages + (size_t)(s / 64) * page_elems + ((size_t)h * 64 + s % 64) * hd;
-    __nv_bfloat16* vdst = kdst + (size_t)H * 64 * hd;
-    const __nv_bfloat16* kp = kv + (size_t)s * kv_stride + (size_t)h * dim;
-    const __nv_bfloat16* vp = kv + (size_t)s * kv_stride + (size_t)H * dim + (size_t)h * hd;
-    const __nv_bfloat16* kr = rows + (size_t)s * width + rank;
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        kdst[d] = d < dim ? kp[d] : kr[d - dim];
-        vdst[d] = vp[d];
-    }
+    __nv_bfloat16* dst = pages + (size_t)(s / 64) * page_elems + (size_t)kvsel * H * 64 * hd + ((size_t)h * 64 + s % 64) * hd + c * 8;
+    const __nv_bfloat16* src;
+    if (kvsel) src = kv + (size_t)s * kv_stride + (size_t)H * dim + (size_t)h * hd + c * 8;
+    else if (c * 8 < dim) src = kv + (size_t)s * kv_stride + (size_t)h * dim + c * 8;
+    else src = kr + (size_t)s * rot + (c * 8 - dim);
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
 }
 
 // q[t, h, off + 2i], q[t, h, off + 2i + 1] turn by cos_sin[t, i] for i < rot_dims / 2, in place.
@@ -439,31 +465,32 @@ extern "C" int bg_latent_attention_partial(const void* q_lat, int ql_dtype, long
 extern "C" int bg_latent_attention_merge(const float* part_o, const float* part_ml, const int* positions, void* out,
                                          int out_dtype, long long out_head, int out_row, int T, int H, int rank,
                                          int max_splits, int split, cudaStream_t stream) {
-    const long long warps = (long long)T * H;
-    if (warps <= 0) return BG_OK;
-    const unsigned blocks = (unsigned)((warps + 7) / 8);
+    const long long blocks = (long long)T * H;
+    if (blocks <= 0) return BG_OK;
+    if (blocks > 0x7fffffffLL || max_splits > 8192) return BG_ERR_SHAPE;
     BG_DISPATCH_DTYPE(out_dtype, TO,
-        launch(latent_attention_merge_kernel<TO>, dim3(blocks), dim3(256), 0, stream, part_o, part_ml, positions, (TO*)out,
-               out_head, out_row, T, H, rank, max_splits, split));
+        launch(latent_attention_merge_kernel<TO>, dim3((unsigned)blocks), dim3(LAT_MERGE_THREADS), (size_t)max_splits * sizeof(float),
+               stream, part_o, part_ml, positions, (TO*)out, out_head, out_row, T, H, rank, max_splits, split));
     BG_LAUNCH_CHECK();
     return BG_OK;
 }
 
 extern "C" int bg_latent_gather(const void* pool, const int* block_table, int max_pages, int req, int num_pages, int page_size,
-                                int width, int S, void* out, cudaStream_t stream) {
+                                int rank, int rot, int S, void* lat, void* kr, cudaStream_t stream) {
     if (S <= 0) return BG_OK;
-    launch(latent_gather_kernel, dim3(S), dim3(128), 0, stream, (const __nv_bfloat16*)pool, block_table, max_pages, req, num_pages,
-           page_size, width, S, (__nv_bfloat16*)out);
+    launch(latent_gather_kernel, dim3(S), dim3(64), 0, stream, (const __nv_bfloat16*)pool, block_table, max_pages, req, num_pages,
+           page_size, rank, rot, S, (__nv_bfloat16*)lat, (__nv_bfloat16*)kr);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }
 
-extern "C" int bg_latent_expand(const void* kv, int kv_stride, const void* rows, int width, int rank, int H, int dim, int rot,
-                                int S, void* pages, cudaStream_t stream) {
+extern "C" int bg_latent_expand(const void* kv, int kv_stride, const void* kr, int H, int dim, int rot, int S, void* pages,
+                                cudaStream_t stream) {
     if (S <= 0) return BG_OK;
-    if (H <= 0 || H > 65535 || width != rank + rot) return BG_ERR_SHAPE;
-    launch(latent_expand_kernel, dim3(S, H), dim3(64), 0, stream, (const __nv_bfloat16*)kv, kv_stride, (const __nv_bfloat16*)rows,
-           width, rank, H, dim, rot, S, (__nv_bfloat16*)pages);
+    if (H <= 0 || dim % 8 != 0 || rot % 8 != 0 || kv_stride % 8 != 0) return BG_ERR_SHAPE;
+    const size_t n = (size_t)S * H * 2 * ((dim + rot) / 8);
+    launch(latent_expand_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const __nv_bfloat16*)kv, kv_stride,
+           (const __nv_bfloat16*)kr, H, dim, rot, S, (__nv_bfloat16*)pages);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

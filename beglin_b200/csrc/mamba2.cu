@@ -1,6 +1,6 @@
 // The Mamba-2 recurrence for a ragged step: every request brings a run of consecutive tokens (a prompt
 // portion or one decoded token) and owns one slot of fixed state, float32:
-//   slot = [ S: heads x N x P | conv: (taps - 1) x channels ]
+//   slot = [ S: heads x P x N | conv: (taps - 1) x channels ]
 // S is the state of the recurrence, conv the last taps-1 inputs of the causal convolution (oldest first).
 // A slot is zero when its request starts, so a convolution that reaches back beyond a sequence's first
 // token finds zeros there.  Four kernels: the convolution with SiLU, the update of its state, the scan, and the gate
@@ -158,7 +158,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restric
 #pragma unroll
     for (int k = 0; k < NPT; ++k) {
         const int nn = RUNS ? ((k >> 2) * NS + ns) * 4 + (k & 3) : ns + k * NS;
-        S[k] = (live && nn < N) ? st[(size_t)nn * P + pcol] : 0.0f;
+        S[k] = (live && nn < N) ? st[(size_t)pcol * N + nn] : 0.0f;
     }
     const float a = expf(to_float(A_log[h]));
     const float bias = to_float(dt_bias[h]);
@@ -231,7 +231,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restric
 #pragma unroll
     for (int k = 0; k < NPT; ++k) {
         const int nn = RUNS ? ((k >> 2) * NS + ns) * 4 + (k & 3) : ns + k * NS;
-        if (live && nn < N) st[(size_t)nn * P + pcol] = S[k];
+        if (live && nn < N) st[(size_t)pcol * N + nn] = S[k];
     }
 }
 

@@ -80,8 +80,9 @@ _SIGNATURES = {
                                         _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
                                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                                         _c_void_p, _c_void_p],
-    "bg_latent_gather": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
-    "bg_latent_expand": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "bg_latent_gather": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+                         _c_void_p],
+    "bg_latent_expand": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "bg_rotate_q": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p],
     "bg_conv_silu": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_ll,
                      _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p],
@@ -1017,35 +1018,38 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, dim: int, rot: in
                                            out.stride(1), T, H, rank, n_splits, split, _stream()), "latent_attention_merge")
 
 
-def latent_gather(pool: torch.Tensor, block_table: torch.Tensor, req: int, S: int, out: torch.Tensor) -> None:
-    """out[s] = the cached row of position s < S of the step's request `req` (zeros where it holds no page); pool
-    [pages, page_size, width] and out [S, width], bfloat16."""
-    _cuda(pool, block_table, out)
+def latent_gather(pool: torch.Tensor, block_table: torch.Tensor, req: int, rank: int, lat: torch.Tensor, kr: torch.Tensor) -> None:
+    """lat[s] and kr[s] = the latent and the rotated key part of the cached row of position s < S of the step's request
+    `req` (zeros where it holds no page); pool [pages, page_size, rank + rot], lat [S, rank], kr [S, rot], bfloat16."""
+    _cuda(pool, block_table, lat, kr)
     _i32(block_table, "block_table")
-    if pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or pool.dim() != 3 or not pool.is_contiguous() \
-            or tuple(out.shape) != (S, pool.shape[2]) or not out.is_contiguous() or not 0 <= req < block_table.shape[0]:
-        raise KernelError("latent_gather: a bfloat16 pool [pages, page, width] and out [S, width]")
+    S, rot = lat.shape[0], pool.shape[2] - rank
+    if pool.dtype != torch.bfloat16 or lat.dtype != torch.bfloat16 or kr.dtype != torch.bfloat16 or pool.dim() != 3 \
+            or not pool.is_contiguous() or tuple(lat.shape) != (S, rank) or tuple(kr.shape) != (S, rot) \
+            or not lat.is_contiguous() or not kr.is_contiguous() or not 0 <= req < block_table.shape[0]:
+        raise KernelError("latent_gather: a bfloat16 pool [pages, page, rank + rot], lat [S, rank] and kr [S, rot]")
     with phase("kv_expand"):
         _check(lib().bg_latent_gather(_p(pool), _p(block_table), block_table.shape[1], req, pool.shape[0], pool.shape[1],
-                                      pool.shape[2], S, _p(out), _stream()), "latent_gather")
+                                      rank, rot, S, _p(lat), _p(kr), _stream()), "latent_gather")
 
 
-def latent_expand(kv: torch.Tensor, rows: torch.Tensor, rank: int, H: int, dim: int, rot: int, pages: torch.Tensor) -> None:
+def latent_expand(kv: torch.Tensor, kr: torch.Tensor, H: int, dim: int, pages: torch.Tensor) -> None:
     """Per-head keys and values of S positions laid out as pages of 64 positions for the grouped-query kernels:
-    kv [S, H dim + H (dim + rot)] = [plain key parts | values], rows [S, rank + rot] (the rotated key part behind
-    the latent); pages [ceil(S / 64), 2, H, 64, dim + rot] receives keys [plain | rotated part] and values."""
-    _cuda(kv, rows, pages)
-    S, hd = kv.shape[0], dim + rot
-    for t in (kv, rows, pages):
+    kv [S, H dim + H (dim + rot)] = [plain key parts | values], kr [S, rot] the rotated key part; pages
+    [ceil(S / 64), 2, H, 64, dim + rot] receives keys [plain | rotated part] and values.  dim and rot are multiples of 8."""
+    _cuda(kv, kr, pages)
+    S, rot = kv.shape[0], kr.shape[1]
+    hd = dim + rot
+    for t in (kv, kr, pages):
         if t.dtype != torch.bfloat16:
             raise KernelError("latent_expand takes bfloat16 tensors")
-    if kv.stride(1) != 1 or kv.shape[1] != H * dim + H * hd or tuple(rows.shape) != (S, rank + rot) or not rows.is_contiguous():
-        raise KernelError(f"latent_expand: kv is {tuple(kv.shape)}, rows {tuple(rows.shape)}")
+    if kv.stride(1) != 1 or kv.shape[1] != H * dim + H * hd or kr.shape[0] != S or not kr.is_contiguous() or dim % 8 or rot % 8 \
+            or kv.stride(0) % 8 or kv.data_ptr() % 16:
+        raise KernelError(f"latent_expand: kv is {tuple(kv.shape)}, kr {tuple(kr.shape)}")
     if tuple(pages.shape) != (-(-S // 64), 2, H, 64, hd) or not pages.is_contiguous():
         raise KernelError(f"latent_expand: pages are {tuple(pages.shape)}")
     with phase("kv_expand"):
-        _check(lib().bg_latent_expand(_p(kv), kv.stride(0), _p(rows), rank + rot, rank, H, dim, rot, S, _p(pages), _stream()),
-               "latent_expand")
+        _check(lib().bg_latent_expand(_p(kv), kv.stride(0), _p(kr), H, dim, rot, S, _p(pages), _stream()), "latent_expand")
 
 
 def rotate_q(q: torch.Tensor, H: int, head: int, off: int, rot_dims: int, cos_sin: torch.Tensor) -> None:
@@ -1094,7 +1098,7 @@ def conv_silu(src: torch.Tensor, col0: int, channels: int, weight: torch.Tensor,
 def ssm_scan(xbc: torch.Tensor, src: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor,
              state: torch.Tensor, slots: torch.Tensor, reqs: torch.Tensor, n_req: int, y: torch.Tensor, H: int, P: int,
              N: int, G: int) -> None:
-    """The recurrence over each request's rows, from and into the slots' state S [H, N, P] (float32, at the start of
+    """The recurrence over each request's rows, from and into the slots' state S [H, P, N] (float32, at the start of
     a slot): dt = softplus(src[t, dt_col + h] + dt_bias[h]); S = exp(-exp(A_log[h]) dt) S + dt B_t x_t^T;
     y_t = S^T C_t + D[h] x_t.  xbc float32 [T, H P + 2 G N] = [x | B | C]; y float32 [T, H P]."""
     _cuda(xbc, src, dt_bias, A_log, D, state, slots, reqs, y)

@@ -43,6 +43,66 @@ __global__ void add_layernorm_kernel(float* __restrict__ x, const TD* __restrict
         o[i] = from_float<TO>((row_buf[i] - mean) * inv * to_float(w[i]));
 }
 
+// The same for a width that is a multiple of 8 with rows on 16-byte boundaries: a thread holds up to ITER runs of eight
+// features in registers, all its loads (the row and every partial sum) on their way together, so a row is one round
+// trip to memory instead of one per 256 features.  256 threads; d <= 2048 ITER.
+template <typename TD, typename TW, typename TO, int ITER>
+__global__ void __launch_bounds__(256)
+add_layernorm_vec8_kernel(float* __restrict__ x, const TD* __restrict__ delta, int parts, size_t part_stride,
+                          const TW* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ rows, int d,
+                          int update) {
+    __shared__ float red[32];
+    pdl_launch();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float* xr = x + (size_t)s * d;
+    const int d8 = d / 8;
+    float v[ITER][8];
+    float sum = 0.0f;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+        const int c = threadIdx.x + it * 256;
+        if (c < d8) {
+            load8(xr + c * 8, v[it]);
+            for (int pp = 0; pp < parts; ++pp) {
+                float dv[8];
+                load8(delta + (size_t)pp * part_stride + (size_t)s * d + c * 8, dv);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[it][k] += dv[k];
+            }
+            if (update) store8(xr + c * 8, v[it]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) sum += v[it][k];
+        }
+    }
+    sum = block_sum(sum, red);
+    const float mean = sum / (float)d;
+    float sq = 0.0f;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+        const int c = threadIdx.x + it * 256;
+        if (c < d8) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { const float dv = v[it][k] - mean; sq += dv * dv; }
+        }
+    }
+    sq = block_sum(sq, red);
+    const float inv = 1.0f / sqrtf(sq / (float)d + eps);
+    TO* o = out + (size_t)r * d;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+        const int c = threadIdx.x + it * 256;
+        if (c < d8) {
+            float wv[8], ov[8];
+            load8(w + c * 8, wv);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ov[k] = (v[it][k] - mean) * inv * wv[k];
+            store8(o + c * 8, ov);
+        }
+    }
+}
+
 // The depth-weighted average behind a layer.  With v = x + sum_p delta[p] (the layer's result):
 //   history[terms - 1] = v;   x = sum_{j < terms} w[j] * history[j], added in the order of j.
 // history is [slots][n] with hist_stride elements between slots; slots 0 .. terms-2 were written earlier.
@@ -60,6 +120,33 @@ __global__ void depth_mix_kernel(float* __restrict__ x, const TD* __restrict__ d
     float acc = 0.0f;
     for (int j = 0; j + 1 < terms; ++j) acc = fmaf(to_float(w[j]), history[(size_t)j * hist_stride + i], acc);
     x[i] = fmaf(to_float(w[terms - 1]), v, acc);
+}
+
+// The same, four values a thread with 16-byte accesses (n a multiple of 4, everything on 16-byte boundaries, float or
+// no delta): the loads of all terms are independent of one another.
+template <typename TW>
+__global__ void depth_mix_vec4_kernel(float* __restrict__ x, const float* __restrict__ delta, int parts, size_t part_stride,
+                                      float* __restrict__ history, size_t hist_stride, const TW* __restrict__ w, int terms,
+                                      size_t n4) {
+    pdl_launch();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    float4 v = reinterpret_cast<const float4*>(x)[i];
+    if (delta) {
+        const float4 dsum = sum_parts4(reinterpret_cast<const float4*>(delta) + i, parts, part_stride / 4);
+        v.x += dsum.x; v.y += dsum.y; v.z += dsum.z; v.w += dsum.w;
+    }
+    reinterpret_cast<float4*>(history + (size_t)(terms - 1) * hist_stride)[i] = v;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int j = 0; j + 1 < terms; ++j) {
+        const float wj = to_float(w[j]);
+        const float4 hj = reinterpret_cast<const float4*>(history + (size_t)j * hist_stride)[i];
+        acc.x = fmaf(wj, hj.x, acc.x); acc.y = fmaf(wj, hj.y, acc.y); acc.z = fmaf(wj, hj.z, acc.z); acc.w = fmaf(wj, hj.w, acc.w);
+    }
+    const float wl = to_float(w[terms - 1]);
+    acc.x = fmaf(wl, v.x, acc.x); acc.y = fmaf(wl, v.y, acc.y); acc.z = fmaf(wl, v.z, acc.z); acc.w = fmaf(wl, v.w, acc.w);
+    reinterpret_cast<float4*>(x)[i] = acc;
 }
 
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
@@ -142,6 +229,29 @@ __global__ void gate_heads_kernel(const TI* __restrict__ src, size_t src_head_st
     out[i] = from_float<TO>(to_float(src[(size_t)h * src_head_stride + (size_t)t * src_row_stride + j]) * s);
 }
 
+// The same, eight features a thread (vd a multiple of 8, rows on 16-byte boundaries).
+template <typename TI, typename TG, typename TO>
+__global__ void gate_heads_vec8_kernel(const TI* __restrict__ src, size_t src_head_stride, int src_row_stride,
+                                       const TG* __restrict__ gate, int gate_stride, int gate_col0, TO* __restrict__ out,
+                                       int T, int H, int vd) {
+    pdl_launch();
+    pdl_wait();
+    const int v8 = vd / 8;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t n = (size_t)T * H * v8;
+    if (i >= n) return;
+    const int j = (int)(i % v8);
+    const int h = (int)((i / v8) % H);
+    const int t = (int)(i / ((size_t)v8 * H));
+    const float g = to_float(gate[(size_t)t * gate_stride + gate_col0 + h]);
+    const float sg = 1.0f / (1.0f + expf(-g));
+    float v[8];
+    load8(src + (size_t)h * src_head_stride + (size_t)t * src_row_stride + j * 8, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] *= sg;
+    store8(out + ((size_t)t * H + h) * vd + j * 8, v);
+}
+
 }  // namespace bg
 
 using namespace bg;
@@ -151,6 +261,18 @@ static int add_layernorm_out(float* x, const void* delta, int parts, size_t part
                              int out_dtype, const int* rows, int n_rows, int d, int update, cudaStream_t stream) {
     const size_t smem = (size_t)d * sizeof(float);
     if (smem > 200 * 1024) return BG_ERR_SHAPE;
+    const bool vec = (d % 8 == 0) && (part_stride % 8 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)delta % 16 == 0) &&
+                     ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0) && d <= 8192;
+    if (vec) {
+        const int iter = (d / 8 + 255) / 256;
+        BG_DISPATCH_DTYPE(out_dtype, TO, {
+            if (iter <= 1) launch(add_layernorm_vec8_kernel<TD, TW, TO, 1>, dim3(n_rows), dim3(256), 0, stream, x, (const TD*)delta, parts, part_stride, (const TW*)w, eps, (TO*)out, rows, d, update);
+            else if (iter <= 2) launch(add_layernorm_vec8_kernel<TD, TW, TO, 2>, dim3(n_rows), dim3(256), 0, stream, x, (const TD*)delta, parts, part_stride, (const TW*)w, eps, (TO*)out, rows, d, update);
+            else launch(add_layernorm_vec8_kernel<TD, TW, TO, 4>, dim3(n_rows), dim3(256), 0, stream, x, (const TD*)delta, parts, part_stride, (const TW*)w, eps, (TO*)out, rows, d, update);
+        });
+        BG_LAUNCH_CHECK();
+        return BG_OK;
+    }
     BG_DISPATCH_DTYPE(out_dtype, TO, {
         auto kern = add_layernorm_kernel<TD, TW, TO>;
         if (smem > BG_SMEM_OPT_IN) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -178,6 +300,15 @@ extern "C" int bg_depth_mix(float* x, const void* delta, int delta_dtype, int pa
     if (n <= 0) return BG_OK;
     if (terms < 1) return BG_ERR_SHAPE;
     if (!delta) { delta_dtype = BG_DTYPE_F32; parts = 0; }
+    if (delta_dtype == BG_DTYPE_F32 && n % 4 == 0 && hist_stride % 4 == 0 && part_stride % 4 == 0 && (uintptr_t)x % 16 == 0 &&
+        (uintptr_t)delta % 16 == 0 && (uintptr_t)history % 16 == 0) {
+        const size_t n4 = (size_t)n / 4;
+        BG_DISPATCH_DTYPE(w_dtype, TW,
+            launch(depth_mix_vec4_kernel<TW>, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, stream, x, (const float*)delta, parts,
+                   (size_t)part_stride, history, (size_t)hist_stride, (const TW*)w, terms, n4));
+        BG_LAUNCH_CHECK();
+        return BG_OK;
+    }
     const unsigned blocks = (unsigned)((n + 255) / 256);
     BG_DISPATCH_DTYPE(delta_dtype, TD, BG_DISPATCH_DTYPE(w_dtype, TW,
         launch(depth_mix_kernel<TD, TW>, dim3(blocks), dim3(256), 0, stream, x, (const TD*)delta, parts, (size_t)part_stride,
@@ -228,6 +359,14 @@ extern "C" int bg_gate_heads(const void* src, int src_dtype, long long src_head_
                              cudaStream_t stream) {
     const long long n = (long long)T * H * vd;
     if (n <= 0) return BG_OK;
+    if (vd % 8 == 0 && src_head_stride % 8 == 0 && src_row_stride % 8 == 0 && (uintptr_t)src % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        const size_t n8 = (size_t)n / 8;
+        BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(gate_dtype, TG, BG_DISPATCH_DTYPE(out_dtype, TO,
+            launch(gate_heads_vec8_kernel<TI, TG, TO>, dim3((unsigned)((n8 + 255) / 256)), dim3(256), 0, stream, (const TI*)src,
+                   (size_t)src_head_stride, src_row_stride, (const TG*)gate, gate_stride, gate_col0, (TO*)out, T, H, vd))));
+        BG_LAUNCH_CHECK();
+        return BG_OK;
+    }
     const unsigned blocks = (unsigned)((n + 255) / 256);
     BG_DISPATCH_DTYPE(src_dtype, TI, BG_DISPATCH_DTYPE(gate_dtype, TG, BG_DISPATCH_DTYPE(out_dtype, TO,
         launch(gate_heads_kernel<TI, TG, TO>, dim3(blocks), dim3(256), 0, stream, (const TI*)src, (size_t)src_head_stride,

@@ -99,6 +99,7 @@ class LatentAttention:
         self.expand = None
         hd = spec.dim + spec.rot_dim
         if not self.f32 and ctx.cache_dtype == torch.bfloat16 and spec.vdim == hd and hd in (64, 128) \
+                and spec.dim % 8 == 0 and spec.rot_dim % 8 == 0 \
                 and ctx.attention in ("auto", "tcgen05"):
             kernel, bq, tile = ops.attention_plan(1, hd, torch.bfloat16, False, ctx.attention, 64)
             if kernel == "tc_rows":
@@ -124,13 +125,14 @@ class LatentAttention:
         s, ctx = self.spec, self.ctx
         T, H, hd = batch.n_rows, s.n_heads, s.dim + s.rot_dim
         S = batch.max_position + 1                                      # every position the portion's rows may see
-        rows = torch.empty((S, s.kv_rank + s.rot_dim), dtype=torch.bfloat16, device=q.device)
-        ops.latent_gather(cache.pool, cache.block_table, 0, S, rows)
+        lat = torch.empty((S, s.kv_rank), dtype=torch.bfloat16, device=q.device)
+        kr = torch.empty((S, s.rot_dim), dtype=torch.bfloat16, device=q.device)
+        ops.latent_gather(cache.pool, cache.block_table, 0, s.kv_rank, lat, kr)
         with ops.phase("kv_expand"):
-            kv = torch.mm(rows[:, :s.kv_rank], self.kv_up.t())          # [S, H dim | H vdim]
+            kv = torch.mm(lat, self.kv_up.t())                          # [S, H dim | H vdim]
         pages = torch.empty((-(-S // 64), 2, H, 64, hd), dtype=torch.bfloat16, device=q.device)
         pages[-1].zero_()                                               # what lies behind position S - 1 in the last page
-        ops.latent_expand(kv, rows, s.kv_rank, H, s.dim, s.rot_dim, pages)
+        ops.latent_expand(kv, kr, H, s.dim, pages)
         if self.rot_dims:
             ops.rotate_q(q, H, hd, s.dim, self.rot_dims, cos_sin)
         table = torch.arange(pages.shape[0], dtype=torch.int32, device=q.device).view(1, -1)

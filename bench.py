@@ -415,7 +415,25 @@ def design_point(cfg, pk, batch, context, steps, warmup, tokens):
     return out
 
 
+def design_timeline(args):
+    """The kernels of one decoding step (or of one prompt step of 2,048 tokens) of the design at the first of the sizes."""
+    from beglin_b200 import Engine
+    width, heads, layers = DESIGN_SIZES[args.design_sizes.split(",")[0]]
+    eng = Engine.random(sukisun_config(width, heads, layers), seed=0, dtype="bfloat16", device="cuda:0",
+                        max_tokens=args.batch * (args.context + 64), page_size=64, max_requests=args.batch,
+                        max_context=args.context + 64)
+    if args.timeline == "prefill":
+        rows = prefill_timeline(eng, 2048, seed=3)
+        print_timeline(rows, layers)
+        print_busy(rows)
+    else:
+        print_timeline(decode_timeline(eng, args.batch, args.context, seed=1), layers)
+    return 0
+
+
 def design_comparison(args, pk):
+    if args.timeline:
+        return design_timeline(args)
     clocks = ClockSampler()
     clocks.start()
     rows = {}
