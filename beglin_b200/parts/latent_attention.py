@@ -171,9 +171,10 @@ class LatentAttention:
         if qblk is None:                                                # a decoding graph's batch keeps its list implicit
             batch.implicit_blocks = False
             qblk, n_qblk = batch.query_blocks(bq)
+        split = ctx.kv_split
         o_lat = torch.empty((H, T, s.kv_rank), dtype=ctx.compute_dtype, device=h.device)
         ops.latent_attention(q_lat, q, s.dim, s.rot_dim, self.rot_dims, cos_sin, cache.pool, cache.block_table,
-                             batch.positions, qblk, n_qblk, batch.max_position, bq, hc, self.tile, ctx.kv_split,
+                             batch.positions, qblk, n_qblk, batch.max_position, bq, hc, self.tile, split,
                              self.scale, o_lat, ctx.status, mma_stages=stages)
         v = self._per_head(o_lat, self.v_up, ctx.compute_dtype)        # [H, T, vdim]
         out = torch.empty((T, H * s.vdim), dtype=ctx.compute_dtype, device=h.device)
