@@ -354,8 +354,6 @@ extern "C" int bg_latent_attention_mma_partial(const float* q_lat, long long ql_
     const size_t half_sm = 110 * 1024, whole_sm = 200 * 1024;
     const size_t s1 = latent_mma_smem(rows, width, 1), s2 = latent_mma_smem(rows, width, 2);
     stages = s2 <= half_sm ? 2 : (s1 <= half_sm ? 1 : (s2 <= whole_sm ? 2 : 1));
-    // a grid of no more CTAs than SMs has nobody to share an SM with: two tiles in flight where they fit
-    if ((long long)n_qblk * chunks * n_splits_launch <= sm_count() && s2 <= whole_sm) stages = 2;
     p.stages = stages;
     const size_t smem = latent_mma_smem(rows, width, stages);
     if (smem > 227 * 1024) return BG_ERR_UNSUPPORTED;

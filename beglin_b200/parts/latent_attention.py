@@ -34,6 +34,7 @@ from .linear import Linear
 from .registry import register_mixer
 from .rope import shared_position
 from .spec import LatentAttentionSpec, TensorRole
+from .stream import NormedInput, ResidualStream
 
 
 @register_mixer("latent_attention")
@@ -147,7 +148,13 @@ class LatentAttention:
         ops.gate_heads(att.view(T, H, hd).transpose(0, 1), down, self.gate_col, out)
         return out
 
-    def forward(self, h: torch.Tensor, batch, cache: PagedKVView) -> torch.Tensor:
+    takes_stream = True        # forward takes a NormedInput and may add its result to the stream itself
+
+    def forward(self, h, batch, cache: PagedKVView, stream: Optional[ResidualStream] = None) -> Optional[torch.Tensor]:
+        """h: the normed rows, or a NormedInput.  With `stream` the result is added to it (in steps of few tokens by the
+        output product itself) or left owed to it, and None is returned; without, the addend is returned."""
+        if isinstance(h, NormedInput):
+            h = h.tensor()
         s, ctx = self.spec, self.ctx
         T, H = batch.n_rows, s.n_heads
         down = self.down(h, out_dtype=torch.float32)                    # [T, q_rank (+ kv_rank + rot) (+ H)]
@@ -161,7 +168,7 @@ class LatentAttention:
             ops.rmsnorm_slice(down, 0, s.q_rank, self.q_norm, s.eps, cq)
         q = self.q_up(cq)                                               # [T, H (dim + rot)]
         if self.expand is not None and batch.n_req == 1 and T >= self.EXPAND_ROWS:
-            return self.o_proj.partial(self._per_head_keys(q, down, cos_sin, batch, cache))
+            return self._result(self._per_head_keys(q, down, cos_sin, batch, cache), stream)
         q_plain = q.view(T, H, s.dim + s.rot_dim)[:, :, :s.dim].transpose(0, 1)          # [H, T, dim]
         q_lat = self._per_head(q_plain, self.k_up_t, torch.float32)    # [H, T, kv_rank] float
         hc, bq, stages = (self.hc, self.bq, 0) if self.mma is None else self.mma
@@ -182,4 +189,10 @@ class LatentAttention:
             ops.gate_heads(v, down, self.gate_col, out)
         else:
             out.view(T, H, s.vdim).copy_(v.transpose(0, 1))
-        return self.o_proj.partial(out)
+        return self._result(out, stream)
+
+    def _result(self, heads: torch.Tensor, stream: Optional[ResidualStream]) -> Optional[torch.Tensor]:
+        if stream is None:
+            return self.o_proj.partial(heads)
+        self.o_proj.into(heads, stream)
+        return None

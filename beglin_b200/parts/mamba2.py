@@ -13,7 +13,7 @@ enters the recurrence is float in both number formats.
 """
 from __future__ import annotations
 
-from typing import Dict, List
+from typing import Dict, List, Optional
 
 import torch
 
@@ -23,6 +23,7 @@ from .context import BuildContext
 from .linear import Linear
 from .registry import register_mixer
 from .spec import Mamba2Spec, TensorRole
+from .stream import NormedInput, ResidualStream
 
 
 def _sizes(spec: Mamba2Spec):
@@ -69,7 +70,13 @@ class Mamba2:
         self.norm_w = ctx.vector(tensors["norm.weight"])
         self.conv_off = spec.n_heads * spec.state * spec.vdim
 
-    def forward(self, h: torch.Tensor, batch, cache: FixedStateView) -> torch.Tensor:
+    takes_stream = True        # forward takes a NormedInput and may add its result to the stream itself
+
+    def forward(self, h, batch, cache: FixedStateView, stream: Optional[ResidualStream] = None) -> Optional[torch.Tensor]:
+        """h: the normed rows, or a NormedInput.  With `stream` the result is added to it (or left owed to it) and None
+        is returned; without, the addend is returned."""
+        if isinstance(h, NormedInput):
+            h = h.tensor()
         s, ctx = self.spec, self.ctx
         T = batch.n_rows
         proj = self.in_proj(h, out_dtype=torch.float32)                 # [T, z | x B C | dt]
@@ -82,4 +89,7 @@ class Mamba2:
                      reqs, n_req, y, s.n_heads, s.vdim, s.state, s.groups)
         out = torch.empty((T, self.inner), dtype=ctx.compute_dtype, device=h.device)
         ops.gated_group_rmsnorm(y, proj, 0, self.norm_w, s.eps, s.norm_groups, out)
-        return self.o_proj.partial(out)
+        if stream is None:
+            return self.o_proj.partial(out)
+        self.o_proj.into(out, stream)
+        return None

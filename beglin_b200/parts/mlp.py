@@ -73,8 +73,17 @@ class DenseAct:
         self.down = Linear(tensors["down.weight"], None, ctx, label="proj_down")
         self.act = ctx.vector(tensors["act"])
 
-    def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
+    takes_stream = True        # forward takes a NormedInput and may add its result to the stream itself
+
+    def forward(self, h, batch, stream: Optional[ResidualStream] = None) -> Optional[torch.Tensor]:
+        """h: the normed rows, or a NormedInput.  With `stream` the result is added to it (or left owed to it) and None
+        is returned; without, the addend is returned."""
+        if not isinstance(h, torch.Tensor):
+            h = h.tensor()
         z = self.up.partial(h)
         a = torch.empty((h.shape[0], self.spec.intermediate), dtype=self.ctx.compute_dtype, device=h.device)
         ops.xielu(z, self.act, a)
-        return self.down.partial(a)
+        if stream is None:
+            return self.down.partial(a)
+        self.down.into(a, stream)
+        return None
