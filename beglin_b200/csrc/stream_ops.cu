@@ -122,31 +122,39 @@ __global__ void depth_mix_kernel(float* __restrict__ x, const TD* __restrict__ d
     x[i] = fmaf(to_float(w[terms - 1]), v, acc);
 }
 
-// The same, four values a thread with 16-byte accesses (n a multiple of 4, everything on 16-byte boundaries, float or
-// no delta): the loads of all terms are independent of one another.
-template <typename TW>
-__global__ void depth_mix_vec4_kernel(float* __restrict__ x, const float* __restrict__ delta, int parts, size_t part_stride,
+// The same, eight values a thread with 16-byte accesses (n a multiple of 8, everything on 16-byte boundaries): the
+// loads of all terms are independent of one another.
+template <typename TD, typename TW>
+__global__ void depth_mix_vec8_kernel(float* __restrict__ x, const TD* __restrict__ delta, int parts, size_t part_stride,
                                       float* __restrict__ history, size_t hist_stride, const TW* __restrict__ w, int terms,
-                                      size_t n4) {
+                                      size_t n8) {
     pdl_launch();
     pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n4) return;
-    float4 v = reinterpret_cast<const float4*>(x)[i];
-    if (delta) {
-        const float4 dsum = sum_parts4(reinterpret_cast<const float4*>(delta) + i, parts, part_stride / 4);
-        v.x += dsum.x; v.y += dsum.y; v.z += dsum.z; v.w += dsum.w;
+    if (i >= n8) return;
+    float v[8];
+    load8(x + i * 8, v);
+    for (int pp = 0; pp < parts; ++pp) {
+        float dv[8];
+        load8(delta + (size_t)pp * part_stride + i * 8, dv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] += dv[k];
     }
-    reinterpret_cast<float4*>(history + (size_t)(terms - 1) * hist_stride)[i] = v;
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    store8(history + (size_t)(terms - 1) * hist_stride + i * 8, v);
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
     for (int j = 0; j + 1 < terms; ++j) {
         const float wj = to_float(w[j]);
-        const float4 hj = reinterpret_cast<const float4*>(history + (size_t)j * hist_stride)[i];
-        acc.x = fmaf(wj, hj.x, acc.x); acc.y = fmaf(wj, hj.y, acc.y); acc.z = fmaf(wj, hj.z, acc.z); acc.w = fmaf(wj, hj.w, acc.w);
+        float hj[8];
+        load8(history + (size_t)j * hist_stride + i * 8, hj);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = fmaf(wj, hj[k], acc[k]);
     }
     const float wl = to_float(w[terms - 1]);
-    acc.x = fmaf(wl, v.x, acc.x); acc.y = fmaf(wl, v.y, acc.y); acc.z = fmaf(wl, v.z, acc.z); acc.w = fmaf(wl, v.w, acc.w);
-    reinterpret_cast<float4*>(x)[i] = acc;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = fmaf(wl, v[k], acc[k]);
+    store8(x + i * 8, acc);
 }
 
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
@@ -300,12 +308,12 @@ extern "C" int bg_depth_mix(float* x, const void* delta, int delta_dtype, int pa
     if (n <= 0) return BG_OK;
     if (terms < 1) return BG_ERR_SHAPE;
     if (!delta) { delta_dtype = BG_DTYPE_F32; parts = 0; }
-    if (delta_dtype == BG_DTYPE_F32 && n % 4 == 0 && hist_stride % 4 == 0 && part_stride % 4 == 0 && (uintptr_t)x % 16 == 0 &&
-        (uintptr_t)delta % 16 == 0 && (uintptr_t)history % 16 == 0) {
-        const size_t n4 = (size_t)n / 4;
-        BG_DISPATCH_DTYPE(w_dtype, TW,
-            launch(depth_mix_vec4_kernel<TW>, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, stream, x, (const float*)delta, parts,
-                   (size_t)part_stride, history, (size_t)hist_stride, (const TW*)w, terms, n4));
+    if (n % 8 == 0 && hist_stride % 8 == 0 && part_stride % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)delta % 16 == 0 &&
+        (uintptr_t)history % 16 == 0) {
+        const size_t n8 = (size_t)n / 8;
+        BG_DISPATCH_DTYPE(delta_dtype, TD, BG_DISPATCH_DTYPE(w_dtype, TW,
+            launch(depth_mix_vec8_kernel<TD, TW>, dim3((unsigned)((n8 + 255) / 256)), dim3(256), 0, stream, x, (const TD*)delta, parts,
+                   (size_t)part_stride, history, (size_t)hist_stride, (const TW*)w, terms, n8)));
         BG_LAUNCH_CHECK();
         return BG_OK;
     }

@@ -71,7 +71,11 @@ class LatentAttention:
                              f"its own width, not {self.rot_dims} features paired '{spec.position.pairing}'")
         # the products of the mixer's input, as ONE: [query latent | key/value latent, key part | gates]
         names = ["q_down.weight"] + (["kv_down.weight"] if spec.own_kv else []) + (["gate.weight"] if spec.gated else [])
-        self.down = Linear(torch.cat([tensors[n] for n in names], dim=0), None, ctx, label="proj_qkv")
+        w_down = torch.cat([tensors[n] for n in names], dim=0)
+        if w_down.shape[0] % 16:                    # rows of zeros up to a multiple of 16 outputs: a width that is no multiple
+            pad = 16 - w_down.shape[0] % 16         # of 8 takes the library's product of many rows off its fast kernels
+            w_down = torch.cat([w_down, torch.zeros((pad, w_down.shape[1]), dtype=w_down.dtype, device=w_down.device)], dim=0)
+        self.down = Linear(w_down, None, ctx, label="proj_qkv")
         self.kv_col = spec.q_rank
         self.gate_col = spec.q_rank + (spec.kv_rank + spec.rot_dim if spec.own_kv else 0)
         self.q_norm = ctx.vector(tensors["q_down.norm"])
