@@ -9,10 +9,12 @@ product per head).  So a step never touches more of the cache than the cached ro
 number of heads.
 
 A step: ONE product of the mixer's input for the query latent, the key/value latent with the key part and
-the gates (the matrices are concatenated at load time); norm of the query latent; norm, rotation and append
-of the key/value latent; the query product; queries into the latent space; attention; values out of the
-latent space; gates; the output product.  A mixer with `own_kv` False has no key/value projection and reads
-the cache of the stage it is told to.
+the gates (the matrices are concatenated at load time, with rows of zeros up to a multiple of 16 outputs);
+ONE kernel for the norm of the query latent and the norm, rotation and append of the key/value latent; the
+query product; queries into the latent space; attention (the queries' rotated part turned inside the kernel)
+and the merge of its splits; values out of the latent space; gates; the output product, which in steps of
+few rows adds into the residual stream itself.  A mixer with `own_kv` False has no key/value projection and
+reads the cache of the stage it is told to.
 
 Long prompt portions in bfloat16 go the other way round where the sizes allow it (dim + rot_dim = vdim = 64 or
 128): the keys and values of all heads are made once per step from the request's cached rows, by ONE product
