@@ -12,6 +12,11 @@
 // maximum subtracted, o = sum_t p_t V_t.  Everything is float.  Because tiles and splits start at
 // absolute positions and a row never shares an accumulator with another row, the result of a row
 // does not depend on how the step was cut or on what else is in the batch.
+//
+// Values may have another size than keys (`vd` features against `hd`): a page then holds the keys of all kv heads,
+// [nkv][page_size][hd], followed by their values, [nkv][page_size][vd].  With `sink` the softmax's denominator is
+// enlarged by one, as if the row saw one more key of score 0 that carries no value: the merge starts its running
+// maximum at 0 and its sum at exp(0 - m), and nothing else changes.
 #include "common.cuh"
 
 namespace bg {
@@ -23,16 +28,17 @@ constexpr int ATT_MAX_DPL = 8;      // head_dim <= 256: at most 8 output feature
 struct AttnParams {
     const void* q;          // [T, nh, hd] with row stride q_stride (elements)
     int q_stride;
-    const void* kv_pool;    // [num_pages][2][nkv][page_size][hd]
+    const void* kv_pool;    // [num_pages] pages of keys [nkv][page_size][hd] followed by values [nkv][page_size][vd]
     int num_pages, page_size;
     const int* block_table; // [B, max_pages]
     int max_pages;
     const int* positions;   // [T]
     const int* qblk;        // [n_qblk][3] = (request, first row, number of rows)
-    float* part_o;          // [T*nh][max_splits][hd]
+    float* part_o;          // [T*nh][max_splits][vd]
     float* part_ml;         // [T*nh][max_splits][2]
     int max_splits;
     int nh, nkv, hd, group;
+    int vd;                 // features of a value (hd in the plain form)
     int window;             // 0: none
     int split;              // keys per split
     int tile;               // keys per shared-memory tile (32 or 64), divides split
@@ -45,16 +51,18 @@ template <typename TQ, typename TC>
 __global__ void __launch_bounds__(ATT_THREADS)
 attention_partial_kernel(AttnParams p) {
     extern __shared__ float smem[];
-    const int hd = p.hd, group = p.group;
+    const int hd = p.hd, vd = p.vd, group = p.group;
     const int kstride = hd + 1;
     const int n_rows_max = p.bq * group;
     float* q_s = smem;                                   // [n_rows_max][hd]
-    float* acc_s = q_s + (size_t)n_rows_max * hd;        // [n_rows_max][hd]
-    float* k_s = acc_s + (size_t)n_rows_max * hd;        // [tile][hd+1]
-    float* v_s = k_s + (size_t)p.tile * kstride;         // [tile][hd]
-    float* m_s = v_s + (size_t)p.tile * hd;              // [n_rows_max]
+    float* acc_s = q_s + (size_t)n_rows_max * hd;        // [n_rows_max][vd]
+    float* k_s = acc_s + (size_t)n_rows_max * vd;        // [tile][hd+1]
+    float* v_s = k_s + (size_t)p.tile * kstride;         // [tile][vd]
+    float* m_s = v_s + (size_t)p.tile * vd;              // [n_rows_max]
     float* l_s = m_s + n_rows_max;                       // [n_rows_max]
-    long long* base_s = (long long*)(l_s + n_rows_max);   // [tile] element offsets (the float count before it is even)
+    // [tile] element offsets of the keys, then [tile] of the values (8-byte aligned: see attention_smem_bytes)
+    long long* base_s = (long long*)(((uintptr_t)(l_s + n_rows_max) + 7) & ~(uintptr_t)7);
+    long long* vbase_s = base_s + p.tile;
 
     pdl_launch();
     pdl_wait();
@@ -75,12 +83,12 @@ attention_partial_kernel(AttnParams p) {
         int r = idx / hd, d = idx - r * hd;
         int qi = r / group, g = r - qi * group;
         q_s[idx] = to_float(q[(size_t)(row0 + qi) * p.q_stride + (size_t)(kvh * group + g) * hd + d]);
-        acc_s[idx] = 0.0f;
     }
+    for (int idx = tid; idx < n_rows * vd; idx += ATT_THREADS) acc_s[idx] = 0.0f;
     for (int r = tid; r < n_rows; r += ATT_THREADS) { m_s[r] = -INFINITY; l_s[r] = 0.0f; }
 
     const TC* pool = (const TC*)p.kv_pool;
-    const size_t page_elems = (size_t)2 * p.nkv * p.page_size * hd;
+    const size_t page_elems = (size_t)p.nkv * p.page_size * (hd + vd);
     const size_t v_off = (size_t)p.nkv * p.page_size * hd;
     const int tile = p.tile;
     const int t_first = (k_begin / tile) * tile;
@@ -90,25 +98,29 @@ attention_partial_kernel(AttnParams p) {
         // element offset of each key's K row in the pool, or -1 for a key outside [k_begin, k_end)
         for (int j = tid; j < tile; j += ATT_THREADS) {
             int key = t0 + j;
-            long long off = -1;
+            long long off = -1, voff = -1;
             if (key >= k_begin && key < k_end) {
                 int page = p.block_table[(size_t)req * p.max_pages + key / p.page_size];
                 if (page < 0 || page >= p.num_pages) {
                     if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE);
                 } else {
                     off = (long long)((size_t)page * page_elems + ((size_t)kvh * p.page_size + key % p.page_size) * hd);
+                    voff = (long long)((size_t)page * page_elems + v_off + ((size_t)kvh * p.page_size + key % p.page_size) * vd);
                 }
             }
             base_s[j] = off;
+            vbase_s[j] = voff;
         }
         __syncthreads();
         for (int idx = tid; idx < tile * hd; idx += ATT_THREADS) {
             int j = idx / hd, d = idx - j * hd;
             long long off = base_s[j];
-            float kv = 0.0f, vv = 0.0f;
-            if (off >= 0) { kv = to_float(pool[off + d]); vv = to_float(pool[off + v_off + d]); }
-            k_s[j * kstride + d] = kv;
-            v_s[j * hd + d] = vv;
+            k_s[j * kstride + d] = off >= 0 ? to_float(pool[off + d]) : 0.0f;
+        }
+        for (int idx = tid; idx < tile * vd; idx += ATT_THREADS) {
+            int j = idx / vd, d = idx - j * vd;
+            long long off = vbase_s[j];
+            v_s[j * vd + d] = off >= 0 ? to_float(pool[off + d]) : 0.0f;
         }
         __syncthreads();
 
@@ -147,11 +159,11 @@ attention_partial_kernel(AttnParams p) {
             }
             psum = warp_sum(psum);
             float acc[ATT_MAX_DPL];
-            float* ar = acc_s + (size_t)r * hd;
+            float* ar = acc_s + (size_t)r * vd;
 #pragma unroll
             for (int i = 0; i < ATT_MAX_DPL; ++i) {
                 int d = i * 32 + lane;
-                acc[i] = (d < hd) ? ar[d] * corr : 0.0f;
+                acc[i] = (d < vd) ? ar[d] * corr : 0.0f;
             }
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
@@ -159,11 +171,11 @@ attention_partial_kernel(AttnParams p) {
                 for (int jj = 0; jj < 32; ++jj) {
                     float pj = __shfl_sync(0xffffffffu, s[c], jj);
                     if (pj != 0.0f) {
-                        const float* vr = v_s + (c * 32 + jj) * hd;
+                        const float* vr = v_s + (c * 32 + jj) * vd;
 #pragma unroll
                         for (int i = 0; i < ATT_MAX_DPL; ++i) {
                             int d = i * 32 + lane;
-                            if (d < hd) acc[i] = fmaf(pj, vr[d], acc[i]);
+                            if (d < vd) acc[i] = fmaf(pj, vr[d], acc[i]);
                         }
                     }
                 }
@@ -171,7 +183,7 @@ attention_partial_kernel(AttnParams p) {
 #pragma unroll
             for (int i = 0; i < ATT_MAX_DPL; ++i) {
                 int d = i * 32 + lane;
-                if (d < hd) ar[d] = acc[i];
+                if (d < vd) ar[d] = acc[i];
             }
             if (lane == 0) { m_s[r] = m_new; l_s[r] = l_s[r] * corr + psum; }
         }
@@ -184,7 +196,7 @@ attention_partial_kernel(AttnParams p) {
         const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
         if (pos < sp * p.split || lo >= (sp + 1) * p.split) continue;
         const size_t prow = ((size_t)(row0 + qi) * p.nh + (size_t)kvh * group + g) * p.max_splits + sp;
-        for (int d = lane; d < hd; d += 32) p.part_o[prow * hd + d] = acc_s[(size_t)r * hd + d];
+        for (int d = lane; d < vd; d += 32) p.part_o[prow * vd + d] = acc_s[(size_t)r * vd + d];
         if (lane == 0) { p.part_ml[prow * 2 + 0] = m_s[r]; p.part_ml[prow * 2 + 1] = l_s[r]; }
     }
 }
@@ -198,7 +210,7 @@ constexpr int MERGE_GROUPS = 4;
 template <typename TO, int DPL, int BATCH>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
-                                       int T, int nh, int hd, int max_splits, int split_arg, int window) {
+                                       int T, int nh, int hd, int max_splits, int split_arg, int window, int sink) {
     pdl_launch();
     pdl_wait();
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -223,10 +235,11 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
     for (int g = 0; g < MERGE_GROUPS; ++g) m = fmaxf(m, ms_r[g]);
     for (int sidx = s_lo + 32 * MERGE_GROUPS + lane; sidx <= s_hi; sidx += 32) m = fmaxf(m, part_ml[(prow + sidx) * 2]);
     m = warp_max(m);
+    if (sink) m = fmaxf(m, 0.0f);
     float acc[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
-    float l = 0.0f;
+    float l = sink ? expf(-m) : 0.0f;
     int grp = 0;
     for (int s0 = s_lo; s0 <= s_hi; s0 += 32, ++grp) {
         // this lane's split of the group of 32: its weight and its share of the sum
@@ -278,20 +291,20 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
 
 using namespace bg;
 
-static size_t attention_smem_bytes(int bq, int group, int hd, int tile) {
+static size_t attention_smem_bytes(int bq, int group, int hd, int vd, int tile) {
     size_t rows = (size_t)bq * group;
-    size_t floats = rows * hd * 2 + (size_t)tile * (hd + 1) + (size_t)tile * hd + rows * 2;
-    return floats * sizeof(float) + (size_t)tile * sizeof(long long) + 8;
+    size_t floats = rows * (hd + vd) + (size_t)tile * (hd + 1) + (size_t)tile * vd + rows * 2;
+    return floats * sizeof(float) + (size_t)2 * tile * sizeof(long long) + 16;
 }
 
 // Rows per query block and keys per tile that fit the shared memory of one CTA for these sizes.
 // Returns 0 and fills bq and tile, or BG_ERR_UNSUPPORTED.
-extern "C" int bg_attention_plan(int group, int hd, int* bq_out, int* tile_out) {
-    if (hd <= 0 || hd > 32 * ATT_MAX_DPL || group <= 0) return BG_ERR_UNSUPPORTED;
+extern "C" int bg_attention_plan(int group, int hd, int vd, int* bq_out, int* tile_out) {
+    if (hd <= 0 || hd > 32 * ATT_MAX_DPL || vd <= 0 || vd > 32 * ATT_MAX_DPL || group <= 0) return BG_ERR_UNSUPPORTED;
     const size_t limit = 200 * 1024;
     for (int tile = 64; tile >= 32; tile >>= 1) {
         for (int bq = 16; bq >= 1; bq >>= 1) {
-            if (attention_smem_bytes(bq, group, hd, tile) <= limit) { *bq_out = bq; *tile_out = tile; return BG_OK; }
+            if (attention_smem_bytes(bq, group, hd, vd, tile) <= limit) { *bq_out = bq; *tile_out = tile; return BG_OK; }
         }
     }
     return BG_ERR_UNSUPPORTED;
@@ -300,17 +313,17 @@ extern "C" int bg_attention_plan(int group, int hd, int* bq_out, int* tile_out) 
 extern "C" int bg_attention_partial(const void* q, int q_dtype, int q_stride, const void* kv_pool, int cache_dtype,
                                     int num_pages, int page_size, const int* block_table, int max_pages,
                                     const int* positions, const int* qblk, int n_qblk, float* part_o, float* part_ml,
-                                    int max_splits, int n_splits_launch, int nh, int nkv, int hd, int window, int split,
+                                    int max_splits, int n_splits_launch, int nh, int nkv, int hd, int vd, int window, int split,
                                     int tile, int bq, float scale, unsigned* status, cudaStream_t stream) {
     if (n_qblk <= 0 || n_splits_launch <= 0) return BG_OK;
-    if (nh % nkv != 0 || hd > 32 * ATT_MAX_DPL || (tile != 32 && tile != 64) || split % tile != 0) return BG_ERR_SHAPE;
+    if (nh % nkv != 0 || hd > 32 * ATT_MAX_DPL || vd <= 0 || vd > 32 * ATT_MAX_DPL || (tile != 32 && tile != 64) || split % tile != 0) return BG_ERR_SHAPE;
     if (n_splits_launch > max_splits || n_splits_launch > 65535 || nkv > 65535) return BG_ERR_SHAPE;
     AttnParams p;
     p.q = q; p.q_stride = q_stride; p.kv_pool = kv_pool; p.num_pages = num_pages; p.page_size = page_size;
     p.block_table = block_table; p.max_pages = max_pages; p.positions = positions; p.qblk = qblk;
-    p.part_o = part_o; p.part_ml = part_ml; p.max_splits = max_splits; p.nh = nh; p.nkv = nkv; p.hd = hd;
+    p.part_o = part_o; p.part_ml = part_ml; p.max_splits = max_splits; p.nh = nh; p.nkv = nkv; p.hd = hd; p.vd = vd;
     p.group = nh / nkv; p.window = window; p.split = split; p.tile = tile; p.bq = bq; p.scale = scale; p.status = status;
-    size_t smem = attention_smem_bytes(bq, p.group, hd, tile);
+    size_t smem = attention_smem_bytes(bq, p.group, hd, vd, tile);
     if (smem > 227 * 1024) return BG_ERR_UNSUPPORTED;
     dim3 grid(n_qblk, nkv, n_splits_launch);
 #define BG_ATT_LAUNCH(TQ, TC)                                                                              \
@@ -337,7 +350,7 @@ extern "C" int bg_attention_partial(const void* q, int q_dtype, int q_stride, co
 template <typename TO, int NS>
 __global__ void attention_merge_few_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
-                                           int T, int nh, int hd, int max_splits, int split_arg, int window) {
+                                           int T, int nh, int hd, int max_splits, int split_arg, int window, int sink) {
     pdl_launch();
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -364,13 +377,13 @@ __global__ void attention_merge_few_kernel(const float* __restrict__ part_o, con
             v[s][i] = (have && d < hd) ? part_o[(prow + s) * hd + d] : 0.0f;
         }
     }
-    float m = -INFINITY;
+    float m = sink ? 0.0f : -INFINITY;
 #pragma unroll
     for (int s = 0; s < NS; ++s) {
         if (s < s_lo || s > s_hi) ms[s] = -INFINITY;          // not written for this row: whatever was read is dropped
         m = fmaxf(m, ms[s]);
     }
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, l = 0.0f;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, l = sink ? expf(-m) : 0.0f;
 #pragma unroll
     for (int s = 0; s < NS; ++s) {                             // in split order
         if (ms[s] != -INFINITY) {
@@ -401,7 +414,7 @@ template <typename TO>
 __global__ void __launch_bounds__(32 * MERGE_WARPS)
 attention_merge_block_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                              const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
-                             int T, int nh, int hd, int max_splits, int split_arg, int window) {
+                             int T, int nh, int hd, int max_splits, int split_arg, int window, int sink) {
     __shared__ float4 acc_s[MERGE_WARPS][32];
     __shared__ float2 ml_s[MERGE_WARPS];
     pdl_launch();
@@ -457,10 +470,10 @@ attention_merge_block_kernel(const float* __restrict__ part_o, const float* __re
     if (lane == 0) ml_s[warp] = make_float2(m, l);
     __syncthreads();
     if (warp != 0) return;
-    float mt = -INFINITY;
+    float mt = sink ? 0.0f : -INFINITY;
 #pragma unroll
     for (int i = 0; i < MERGE_WARPS; ++i) mt = fmaxf(mt, ml_s[i].x);
-    float lt = 0.0f;
+    float lt = sink ? expf(-mt) : 0.0f;
     float4 at = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
     for (int i = 0; i < MERGE_WARPS; ++i) {                     // in warp order
@@ -481,7 +494,7 @@ attention_merge_block_kernel(const float* __restrict__ part_o, const float* __re
 
 extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, const int* positions, void* out,
                                   int out_dtype, int out_stride, int T, int nh, int hd, int max_splits, int split,
-                                  int window, cudaStream_t stream) {
+                                  int window, int sink, cudaStream_t stream) {
     if (T <= 0) return BG_OK;
     long long warps = (long long)T * nh;
     unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
@@ -496,24 +509,24 @@ extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, con
         // 5 us this way; the decode step of the 1.5B sizes went from 1.372 to 1.214 ms at batch 1, from 1.225 to
         // 1.151 ms at batch 2)
         launch(attention_merge_block_kernel<__nv_bfloat16>, dim3((unsigned)warps), dim3(32 * MERGE_WARPS), 0, stream,
-               part_o, part_ml, positions, (__nv_bfloat16*)out, out_stride, T, nh, hd, max_splits, split, window);
+               part_o, part_ml, positions, (__nv_bfloat16*)out, out_stride, T, nh, hd, max_splits, split, window, sink);
     } else if (max_splits <= 8 && hd <= 128) {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 8>, dim3(few_blocks), dim3(few_threads), 0, stream,
-            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
+            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window, sink));
     } else if (max_splits <= 16 && hd <= 128) {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 16>, dim3(few_blocks), dim3(few_threads), 0, stream,
-            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
+            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window, sink));
     } else if (block_fits) {
         // bfloat16 rows of few requests with many splits each (the float path keeps one order of summation for
         // every shape of a step, so that its rows do not depend on the batch)
         launch(attention_merge_block_kernel<__nv_bfloat16>, dim3((unsigned)warps), dim3(32 * MERGE_WARPS), 0, stream,
-               part_o, part_ml, positions, (__nv_bfloat16*)out, out_stride, T, nh, hd, max_splits, split, window);
+               part_o, part_ml, positions, (__nv_bfloat16*)out, out_stride, T, nh, hd, max_splits, split, window, sink);
     } else if (hd <= 128) {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_kernel<TO, 4, 16>, dim3(blocks), dim3(256), 0, stream,
-            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
+            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window, sink));
     } else {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_kernel<TO, ATT_MAX_DPL, 4>, dim3(blocks), dim3(256), 0, stream,
-            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
+            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window, sink));
     }
     BG_LAUNCH_CHECK();
     return BG_OK;

@@ -319,13 +319,20 @@ __global__ void add_residual_kernel(float* __restrict__ x, const TD* __restrict_
 // silu(g) * u.  For a bfloat16 result (8 bits of mantissa) the exponential and the reciprocal are the hardware's
 // approximations (ex2.approx and the approximate division: relative error about 2^-21), which makes the kernel bound by memory
 // instead of by these two functions; a float result is computed with expf and a division.
-template <typename TO> __device__ __forceinline__ float silu_mul(float g, float u);
-template <> __device__ __forceinline__ float silu_mul<float>(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
-template <> __device__ __forceinline__ float silu_mul<__nv_bfloat16>(float g, float u) {
-    return __fdividef(g, 1.0f + __expf(-g)) * u;
+// ACT 0: silu.  ACT 1: the tanh form of GELU, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))), which is
+// g * sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3)); a float result takes tanhf.
+template <typename TO, int ACT> __device__ __forceinline__ float silu_mul(float g, float u) {
+    if constexpr (ACT == 0) {
+        if constexpr (std::is_same<TO, float>::value) return (g / (1.0f + expf(-g))) * u;
+        else return __fdividef(g, 1.0f + __expf(-g)) * u;
+    } else {
+        const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        if constexpr (std::is_same<TO, float>::value) return 0.5f * g * (1.0f + tanhf(z)) * u;
+        else return __fdividef(g, 1.0f + __expf(-2.0f * z)) * u;
+    }
 }
 
-template <typename TI, typename TO>
+template <typename TI, typename TO, int ACT>
 __global__ void swiglu_kernel(const TI* __restrict__ gu, int parts, size_t part_stride, TO* __restrict__ out,
                               int rows, int im, int block) {
     pdl_launch();
@@ -341,12 +348,12 @@ __global__ void swiglu_kernel(const TI* __restrict__ gu, int parts, size_t part_
     if (idle) return;
     float g = sum_parts(gp, parts, part_stride);
     float u = sum_parts(gp + (block > 0 ? block : im), parts, part_stride);
-    out[idx] = from_float<TO>(silu_mul<TO>(g, u));
+    out[idx] = from_float<TO>(silu_mul<TO, ACT>(g, u));
 }
 
 // Float partial sums, im and block multiples of 4: four features per thread, 16-byte loads, the parts added in
 // index order as above.
-template <typename TO>
+template <typename TO, int ACT>
 __global__ void swiglu_parts_vec4_kernel(const float* __restrict__ gu, int parts, size_t part_stride, TO* __restrict__ out,
                                          int rows, int im, int block) {
     pdl_launch();
@@ -361,7 +368,7 @@ __global__ void swiglu_parts_vec4_kernel(const float* __restrict__ gu, int parts
     if (idle) return;
     const float4 g = sum_parts4(gp, parts, part_stride / 4);
     const float4 u = sum_parts4(gp + (block > 0 ? block : im) / 4, parts, part_stride / 4);
-    const float r[4] = {silu_mul<TO>(g.x, u.x), silu_mul<TO>(g.y, u.y), silu_mul<TO>(g.z, u.z), silu_mul<TO>(g.w, u.w)};
+    const float r[4] = {silu_mul<TO, ACT>(g.x, u.x), silu_mul<TO, ACT>(g.y, u.y), silu_mul<TO, ACT>(g.z, u.z), silu_mul<TO, ACT>(g.w, u.w)};
     TO* o = out + (size_t)t * (size_t)im + i;
     if constexpr (std::is_same<TO, float>::value) {
         *reinterpret_cast<float4*>(o) = make_float4(r[0], r[1], r[2], r[3]);
@@ -375,7 +382,7 @@ __global__ void swiglu_parts_vec4_kernel(const float* __restrict__ gu, int parts
 }
 
 // One tensor (no partial sums), im a multiple of 8: eight features per thread, 16-byte accesses.
-template <typename TI, typename TO>
+template <typename TI, typename TO, int ACT>
 __global__ void swiglu_vec8_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int rows, int im, int block) {
     pdl_launch();
     const int im8 = im >> 3;
@@ -391,7 +398,7 @@ __global__ void swiglu_vec8_kernel(const TI* __restrict__ gu, TO* __restrict__ o
     load8(gu + t * 2 * (size_t)im + col, g);
     load8(gu + t * 2 * (size_t)im + col + (block > 0 ? block : im), u);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) g[i] = silu_mul<TO>(g[i], u[i]);
+    for (int i = 0; i < 8; ++i) g[i] = silu_mul<TO, ACT>(g[i], u[i]);
     store8(out + t * (size_t)im + 8 * c, g);
 }
 
@@ -734,7 +741,7 @@ extern "C" int bg_add_residual(float* x, const void* delta, int delta_dtype, lon
     return BG_OK;
 }
 
-template <typename TI>
+template <typename TI, int ACT>
 static int swiglu_in(const void* gu, int parts, size_t part_stride, void* out, int out_dtype, int rows, int im, int block,
                      cudaStream_t stream) {
     const bool small = (size_t)rows * (size_t)im < (1ull << 32);          // the vector kernels count their pieces in 32 bits
@@ -742,18 +749,18 @@ static int swiglu_in(const void* gu, int parts, size_t part_stride, void* out, i
     if (vec) {
         size_t total = (size_t)rows * (im / 8);
         unsigned blocks = (unsigned)((total + 255) / 256);
-        BG_DISPATCH_DTYPE(out_dtype, TO, launch(swiglu_vec8_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream,
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(swiglu_vec8_kernel<TI, TO, ACT>, dim3(blocks), dim3(256), 0, stream,
             (const TI*)gu, (TO*)out, rows, im, block));
     } else if (small && std::is_same<TI, float>::value && (im % 4 == 0) && (block % 4 == 0) && (part_stride % 4 == 0) &&
                ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
         size_t total = (size_t)rows * (im / 4);
         unsigned blocks = (unsigned)((total + 255) / 256);
-        BG_DISPATCH_DTYPE(out_dtype, TO, launch(swiglu_parts_vec4_kernel<TO>, dim3(blocks), dim3(256), 0, stream,
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(swiglu_parts_vec4_kernel<TO, ACT>, dim3(blocks), dim3(256), 0, stream,
             (const float*)gu, parts, part_stride, (TO*)out, rows, im, block));
     } else {
         size_t total = (size_t)rows * im;
         unsigned blocks = (unsigned)((total + 255) / 256);
-        BG_DISPATCH_DTYPE(out_dtype, TO, launch(swiglu_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream,
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(swiglu_kernel<TI, TO, ACT>, dim3(blocks), dim3(256), 0, stream,
             (const TI*)gu, parts, part_stride, (TO*)out, rows, im, block));
     }
     BG_LAUNCH_CHECK();
@@ -761,10 +768,11 @@ static int swiglu_in(const void* gu, int parts, size_t part_stride, void* out, i
 }
 
 extern "C" int bg_swiglu(const void* gu, int in_dtype, int parts, long long part_stride, void* out, int out_dtype,
-                         int rows, int im, int block, cudaStream_t stream) {
+                         int rows, int im, int block, int act, cudaStream_t stream) {
     if (rows <= 0) return BG_OK;
-    if (parts < 1 || block < 0 || (block > 0 && im % block != 0)) return BG_ERR_SHAPE;
-    BG_DISPATCH_DTYPE(in_dtype, TI, return (swiglu_in<TI>(gu, parts, (size_t)part_stride, out, out_dtype, rows, im, block, stream)));
+    if (parts < 1 || block < 0 || (block > 0 && im % block != 0) || act < 0 || act > 1) return BG_ERR_SHAPE;
+    if (act == 0) BG_DISPATCH_DTYPE(in_dtype, TI, return (swiglu_in<TI, 0>(gu, parts, (size_t)part_stride, out, out_dtype, rows, im, block, stream)));
+    else BG_DISPATCH_DTYPE(in_dtype, TI, return (swiglu_in<TI, 1>(gu, parts, (size_t)part_stride, out, out_dtype, rows, im, block, stream)));
     return BG_OK;
 }
 

@@ -1,0 +1,326 @@
+// Routed experts: what stands around the experts' products.
+//
+//   route_topk     per token, the `top` experts of largest score (score = sigmoid of the router's float logit, or the
+//                  logit itself), ties to the lower index; the weight of a choice is its score, divided by the sum of
+//                  the chosen scores when `renorm`.
+//   route_sort     the step's assignments (token t, rank j) -> a = t * top + j are laid out expert by expert:
+//                  offsets[e] .. offsets[e + 1] are expert e's rows; row_of[a] is where assignment a went and
+//                  src_of[row] the assignment that row holds.  ONE CTA; the order inside an expert is whatever the
+//                  atomics give, which no result depends on (a row's product is a function of that row alone).
+//   route_gather   xp[row] = (weight * x[token]) rounded to the compute type (or x[token] as it is).
+//   gemm_grouped   yp[row] = act(xp[row] W[e]^T) on CUDA cores, float accumulation, every output summed over k in index
+//                  order by one thread: the float32 path, and the sizes the tensor-core product does not take.
+//   route_combine  out[t] = sum_j (weight *) yp[row_of[t * top + j]], ranks added in index order, float.
+//
+// Nothing here is read back to the host: the grids depend on the step's shapes alone (the grouped products are launched
+// with as many row tiles as any distribution of the tokens could need, and a CTA without rows returns), so a step with
+// routed experts can be captured in a graph.
+#include "common.cuh"
+
+namespace bg {
+
+__global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E, int top, int sigmoid, int renorm,
+                                  int* __restrict__ ids, float* __restrict__ weights) {
+    extern __shared__ float score_s[];                     // [warps][E]
+    pdl_launch();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    float* sc = score_s + (size_t)warp * E;
+    for (int e = lane; e < E; e += 32) {
+        const float z = logits[(size_t)t * E + e];
+        sc[e] = sigmoid ? 1.0f / (1.0f + expf(-z)) : z;
+    }
+    __syncwarp();
+    float total = 0.0f;
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = sc[e];
+            if (v > best) { best = v; arg = e; }            // ascending e: the first of equal scores stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (lane == 0) {
+            ids[(size_t)t * top + j] = arg;
+            weights[(size_t)t * top + j] = best;
+            sc[arg] = -INFINITY;
+        }
+        total += best;
+        __syncwarp();
+    }
+    if (renorm && lane < top) weights[(size_t)t * top + lane] /= total;
+}
+
+__global__ void __launch_bounds__(1024)
+route_sort_kernel(const int* __restrict__ ids, int A, int E, int* __restrict__ offsets, int* __restrict__ row_of,
+                  int* __restrict__ src_of) {
+    extern __shared__ int count_s[];                       // [E] counts, then [E] cursors
+    int* cursor_s = count_s + E;
+    pdl_launch();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count_s[e] = 0;
+    pdl_wait();
+    __syncthreads();
+    for (int a = threadIdx.x; a < A; a += blockDim.x) {
+        const int e = ids[a];
+        if (e >= 0 && e < E) atomicAdd(&count_s[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) { offsets[e] = run; cursor_s[e] = run; run += count_s[e]; }
+        offsets[E] = run;
+    }
+    __syncthreads();
+    for (int a = threadIdx.x; a < A; a += blockDim.x) {
+        const int e = ids[a];
+        if (e < 0 || e >= E) continue;
+        const int row = atomicAdd(&cursor_s[e], 1);
+        row_of[a] = row;
+        src_of[row] = a;
+    }
+}
+
+template <typename TI, typename TO>
+__global__ void route_gather_kernel(const TI* __restrict__ x, const float* __restrict__ weights, const int* __restrict__ src_of,
+                                    TO* __restrict__ xp, int A, int d, int top, int scale) {
+    pdl_launch();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const int a = src_of[row];
+    const float w = scale ? weights[a] : 1.0f;
+    const TI* src = x + (size_t)(a / top) * d;
+    TO* dst = xp + (size_t)row * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = from_float<TO>(w * to_float(src[i]));
+}
+
+template <typename TY>
+__global__ void route_combine_kernel(const TY* __restrict__ yp, const float* __restrict__ weights, const int* __restrict__ row_of,
+                                     float* __restrict__ out, int T, int d, int top, int scale) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < top; ++j) {
+            const int a = t * top + j;
+            const float v = to_float(yp[(size_t)row_of[a] * d + i]);
+            acc += scale ? weights[a] * v : v;
+        }
+        out[(size_t)t * d + i] = acc;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ grouped product
+// The expert and the rows of row tile `tile` (tiles of `bm` rows, expert after expert); false when there is none.
+__device__ __forceinline__ bool group_tile(const int* offsets, int E, int bm, int tile, int* e_out, int* row0, int* n_rows) {
+    int before = 0;
+    for (int e = 0; e < E; ++e) {
+        const int lo = offsets[e], n = offsets[e + 1] - lo;
+        const int tiles = (n + bm - 1) / bm;
+        if (tile < before + tiles) {
+            const int r = (tile - before) * bm;
+            *e_out = e; *row0 = lo + r; *n_rows = min(bm, n - r);
+            return true;
+        }
+        before += tiles;
+    }
+    return false;
+}
+
+constexpr int GG_BM = 32, GG_BN = 64, GG_BK = 16, GG_THREADS = 256;
+
+// C[row, n] = act(sum_k A[row, k] W[e][n, k]); ACT 1: the square of relu.
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(GG_THREADS)
+gemm_grouped_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw, long long w_expert, TC* __restrict__ C,
+                    int ldc, const int* __restrict__ offsets, int E, int N, int K, int act) {
+    __shared__ float As[GG_BK][GG_BM + 4];
+    __shared__ float Ws[GG_BK][GG_BN + 4];
+    __shared__ int where[3];
+    pdl_launch();
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        int e = -1, r0 = 0, n = 0;
+        if (!group_tile(offsets, E, GG_BM, blockIdx.y, &e, &r0, &n)) e = -1;
+        where[0] = e; where[1] = r0; where[2] = n;
+    }
+    __syncthreads();
+    const int e = where[0], row0 = where[1], n_rows = where[2];
+    if (e < 0) return;
+    W += (size_t)e * w_expert;
+    const int tid = threadIdx.x;
+    const int n0 = blockIdx.x * GG_BN;
+    const int tx = tid & 15, ty = tid >> 4;          // 16 x 16 threads, each 2 rows x 4 columns of C
+    float acc[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += GG_BK) {
+        // A tile: 32 rows x 16 k = 512 values, two a thread; W tile: 64 rows x 16 k = 1024 values, four a thread
+        for (int idx = tid; idx < GG_BM * GG_BK; idx += GG_THREADS) {
+            const int r = idx / GG_BK, k = idx - r * GG_BK;
+            As[k][r] = (r < n_rows && k0 + k < K) ? to_float(A[(size_t)(row0 + r) * lda + k0 + k]) : 0.0f;
+        }
+        for (int idx = tid; idx < GG_BN * GG_BK; idx += GG_THREADS) {
+            const int r = idx / GG_BK, k = idx - r * GG_BK;
+            Ws[k][r] = (n0 + r < N && k0 + k < K) ? to_float(W[(size_t)(n0 + r) * ldw + k0 + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GG_BK; ++kk) {
+            float a[2], w[4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) a[i] = As[kk][ty * 2 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = ty * 2 + i;
+        if (r >= n_rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (act == 1) { v = fmaxf(v, 0.0f); v *= v; }
+            C[(size_t)(row0 + r) * ldc + n] = from_float<TC>(v);
+        }
+    }
+}
+
+// C[M, N] = A[M, K] W[N, K]^T with A of either type and float W and C: the router's logits, float from a step's rows
+// in the compute type.  Every output is summed over k in index order by one thread.
+template <typename TA>
+__global__ void __launch_bounds__(256)
+gemm_rows_f32w_kernel(const TA* __restrict__ A, int lda, const float* __restrict__ W, int ldw, float* __restrict__ C, int ldc,
+                      int M, int N, int K) {
+    __shared__ float As[16][64 + 4];
+    __shared__ float Ws[16][64 + 4];
+    pdl_launch();
+    pdl_wait();
+    const int tid = threadIdx.x, m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    const int tx = tid & 15, ty = tid >> 4;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        for (int idx = tid; idx < 64 * 16; idx += 256) {
+            const int r = idx >> 4, k = idx & 15;
+            As[k][r] = (m0 + r < M && k0 + k < K) ? to_float(A[(size_t)(m0 + r) * lda + k0 + k]) : 0.0f;
+            Ws[k][r] = (n0 + r < N && k0 + k < K) ? W[(size_t)(n0 + r) * ldw + k0 + k] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) {
+            float a[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty * 4 + i]; w[i] = Ws[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+            if (m < M && n < N) C[(size_t)m * ldc + n] = acc[i][j];
+        }
+}
+
+}  // namespace bg
+
+using namespace bg;
+
+extern "C" int bg_route_logits(const void* A, int a_dtype, int lda, const float* W, int ldw, float* C, int ldc, int M, int N,
+                               int K, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return BG_OK;
+    if (K <= 0) return BG_ERR_SHAPE;
+    dim3 grid((N + 63) / 64, (M + 63) / 64);
+    if (grid.y > 65535) return BG_ERR_SHAPE;
+    BG_DISPATCH_DTYPE(a_dtype, TA, launch(gemm_rows_f32w_kernel<TA>, grid, dim3(256), 0, stream, (const TA*)A, lda, W, ldw, C, ldc,
+                                          M, N, K));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_route_topk(const float* logits, int T, int E, int top, int sigmoid, int renorm, int* ids, float* weights,
+                             cudaStream_t stream) {
+    if (T <= 0) return BG_OK;
+    if (E <= 0 || top <= 0 || top > E || top > 32) return BG_ERR_SHAPE;
+    const int warps = 4;
+    const size_t smem = (size_t)warps * E * sizeof(float);
+    if (smem > 40 * 1024) return BG_ERR_UNSUPPORTED;
+    launch(route_topk_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), smem, stream, logits, T, E, top, sigmoid, renorm, ids,
+           weights);
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_route_sort(const int* ids, int A, int E, int* offsets, int* row_of, int* src_of, cudaStream_t stream) {
+    if (E <= 0 || A < 0) return BG_ERR_SHAPE;
+    const size_t smem = (size_t)2 * E * sizeof(int);
+    if (smem > 40 * 1024) return BG_ERR_UNSUPPORTED;
+    launch(route_sort_kernel, dim3(1), dim3(1024), smem, stream, ids, A, E, offsets, row_of, src_of);
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_route_gather(const void* x, int x_dtype, const float* weights, const int* src_of, void* xp, int xp_dtype, int A,
+                               int d, int top, int scale, cudaStream_t stream) {
+    if (A <= 0) return BG_OK;
+    const int threads = d >= 256 ? 256 : ((d + 31) / 32) * 32;
+    BG_DISPATCH_DTYPE(x_dtype, TI, BG_DISPATCH_DTYPE(xp_dtype, TO,
+        launch(route_gather_kernel<TI, TO>, dim3(A), dim3(threads), 0, stream, (const TI*)x, weights, src_of, (TO*)xp, A, d, top, scale)));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_route_combine(const void* yp, int y_dtype, const float* weights, const int* row_of, float* out, int T, int d,
+                                int top, int scale, cudaStream_t stream) {
+    if (T <= 0) return BG_OK;
+    const int threads = d >= 256 ? 256 : ((d + 31) / 32) * 32;
+    BG_DISPATCH_DTYPE(y_dtype, TY, launch(route_combine_kernel<TY>, dim3(T), dim3(threads), 0, stream, (const TY*)yp, weights, row_of,
+                                          out, T, d, top, scale));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+// A [rows, K] (float or bfloat16), W [E][N, K] of the same type with w_expert elements between experts, C [rows, N] float or of
+// A's type.  `rows` is the number of assignments: the grid has a row tile for every tile any distribution could need.
+extern "C" int bg_gemm_grouped(const void* A, int a_dtype, int lda, const void* W, int ldw, long long w_expert, void* C, int c_dtype,
+                               int ldc, const int* offsets, int E, int rows, int N, int K, int act, cudaStream_t stream) {
+    if (rows <= 0 || N <= 0) return BG_OK;
+    if (K <= 0 || E <= 0) return BG_ERR_SHAPE;
+    const int row_tiles = rows / GG_BM + E;
+    if (row_tiles > 65535) return BG_ERR_SHAPE;
+    dim3 grid((N + GG_BN - 1) / GG_BN, row_tiles);
+    if (a_dtype == BG_DTYPE_F32 && c_dtype == BG_DTYPE_F32)
+        launch(gemm_grouped_kernel<float, float, float>, grid, dim3(GG_THREADS), 0, stream, (const float*)A, lda, (const float*)W, ldw,
+               w_expert, (float*)C, ldc, offsets, E, N, K, act);
+    else if (a_dtype == BG_DTYPE_BF16 && c_dtype == BG_DTYPE_BF16)
+        launch(gemm_grouped_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, grid, dim3(GG_THREADS), 0, stream,
+               (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, ldw, w_expert, (__nv_bfloat16*)C, ldc, offsets, E, N, K, act);
+    else if (a_dtype == BG_DTYPE_BF16 && c_dtype == BG_DTYPE_F32)
+        launch(gemm_grouped_kernel<__nv_bfloat16, __nv_bfloat16, float>, grid, dim3(GG_THREADS), 0, stream,
+               (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, ldw, w_expert, (float*)C, ldc, offsets, E, N, K, act);
+    else return BG_ERR_DTYPE;
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}

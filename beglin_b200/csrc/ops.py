@@ -26,17 +26,33 @@ _SIGNATURES = {
     "bg_add_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_float, _c_void_p, _c_int,
                        _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "bg_add_residual": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
-    "bg_swiglu": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_swiglu": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_rope_table": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
     "bg_rope_kv_append": [_c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
                           _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
-    "bg_attention_plan": [_c_int, _c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
+    "bg_attention_plan": [_c_int, _c_int, _c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
     "bg_attention_partial": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int,
                              _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
-                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     "bg_attention_merge": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
-                           _c_int, _c_int, _c_int, _c_void_p],
+                           _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_rmsnorm_add": [_c_void_p, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_int,
+                       _c_int, _c_void_p],
+    "bg_cast_rows": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
+    "bg_qk_norm_rope_append": [_c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
+                               _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int,
+                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "bg_route_logits": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_route_topk": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "bg_route_sort": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "bg_route_gather": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_route_combine": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_gemm_grouped": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
+                        _c_int, _c_int, _c_int, _c_void_p],
+    "bg_gemm_grouped_tc": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
+                           _c_void_p, _c_int, _c_void_p, _c_void_p],
+    "bg_sigmoid_gate": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_void_p],
     "bg_attention_mma_plan": [_c_int, _c_int, _c_int, ctypes.POINTER(_c_int)],
     "bg_attention_mma_partial": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                                  _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -355,9 +371,14 @@ def add_residual(x: torch.Tensor, delta: torch.Tensor) -> None:
         _check(lib().bg_add_residual(_p(x), _p(delta), _dt(delta), x.numel(), _stream()), "add_residual")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
-    """out[t, i] = silu(g[t, i]) * g[t, im + i], g = gate_up or the sum of its partial sums.  With
-    `block` > 0 the columns of g are interleaved in blocks of that many: gate, up, gate, up, ..."""
+GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0, activation: str = "silu") -> None:
+    """out[t, i] = act(g[t, i]) * g[t, im + i], g = gate_up or the sum of its partial sums; act is silu or the tanh form
+    of GELU.  With `block` > 0 the columns of g are interleaved in blocks of that many: gate, up, gate, up, ..."""
+    if activation not in GLU_ACTIVATIONS:
+        raise KernelError(f"swiglu: unknown activation '{activation}' ({', '.join(GLU_ACTIVATIONS)})")
     _cuda(gate_up, out)
     parts, stride = _parts(gate_up, "swiglu: gate_up")
     rows, two_im = gate_up.shape[-2:]
@@ -369,8 +390,8 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
     if block < 0 or (block > 0 and im % block):
         raise KernelError(f"swiglu: blocks of {block} do not divide {im} features")
     with phase("swiglu"):
-        _check(lib().bg_swiglu(_p(gate_up), _dt(gate_up), parts, stride, _p(out), _dt(out), rows, im, block, _stream()),
-               "swiglu")
+        _check(lib().bg_swiglu(_p(gate_up), _dt(gate_up), parts, stride, _p(out), _dt(out), rows, im, block,
+                               GLU_ACTIVATIONS[activation], _stream()), "swiglu")
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
@@ -427,16 +448,22 @@ def attention_wide_from(keys: int = 0) -> int:
 
 
 TC_ROWS_FOR = ("auto", "tcgen05")
+SINK_KERNELS = ("generic",)          # kernels whose softmax can take the enlarged denominator (`sink`)
 
 
 def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, decode_only: bool = False,
-                   prefer: str = "auto", page_size: int = 64) -> Tuple[str, int, int]:
+                   prefer: str = "auto", page_size: int = 64, vd: Optional[int] = None) -> Tuple[str, int, int]:
     """(kernel, rows per query block, keys per tile) for these sizes.  Kernels: "mma_keys" (tensor
     cores, one token per block, for steps of single tokens), "mma_rows" (tensor cores, up to 64 rows
     per block) and "generic" (CUDA cores, every size up to head_dim 256, float or bfloat16)."""
     L = lib()
     if prefer not in ("auto", "generic", "mma", "tcgen05"):
         raise KernelError(f"unknown attention kernel choice '{prefer}'")
+    vd = hd if vd is None else vd
+    if vd != hd:
+        if prefer in ("mma", "tcgen05"):
+            raise KernelError(f"the tensor-core attention kernels take values of the keys' size ({hd}), not {vd}")
+        prefer = "generic"
     if dtype == torch.bfloat16 and not decode_only and prefer in TC_ROWS_FOR:
         bq = _c_int(0)
         if L.bg_attention_tc_plan(group, hd, page_size, ctypes.byref(bq)) == 0:
@@ -453,10 +480,10 @@ def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, deco
             raise KernelError(f"the tensor-core attention kernel does not take head_dim {hd} with {group} query "
                               "heads per kv head (head_dim 64 or 128; at most 64 heads per kv head)")
     bq, tile = _c_int(0), _c_int(0)
-    rc = L.bg_attention_plan(group, hd, ctypes.byref(bq), ctypes.byref(tile))
+    rc = L.bg_attention_plan(group, hd, vd, ctypes.byref(bq), ctypes.byref(tile))
     if rc != 0:
-        raise KernelError(f"attention: head_dim {hd} with {group} query heads per kv head is not supported "
-                          "(head_dim must be at most 256)")
+        raise KernelError(f"attention: head_dim {hd} (values of {vd}) with {group} query heads per kv head is not "
+                          "supported (both sizes must be at most 256)")
     return "generic", bq.value, tile.value
 
 
@@ -498,7 +525,7 @@ def attention(*args, **kwargs) -> None:
 def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table: torch.Tensor,
               positions: torch.Tensor, qblk: torch.Tensor, n_qblk: int, max_position: int, n_rows: int, nh: int,
               nkv: int, hd: int, window: int, split: int, tile: int, bq: int, scale: float, out: torch.Tensor,
-              status: Optional[torch.Tensor], kernel: str = "generic") -> None:
+              status: Optional[torch.Tensor], kernel: str = "generic", vd: Optional[int] = None, sink: bool = False) -> None:
     """Paged grouped-query attention of a step's rows; out is [T, nh*hd].  `kernel`, `bq` and `tile`
     come from `attention_plan`; `qblk` must be cut for that `bq`; `max_position` is the largest
     position among the rows (or a bound on it).
@@ -515,11 +542,22 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
         raise KernelError("attention: only the decoding kernel runs without a list of query blocks (block i = row i)")
     if kernel == "tc_rows" and status is None:
         raise KernelError("attention: the tcgen05 kernel wants a status word (its waits are bounded)")
-    num_pages, two, nkv_, page_size, hd_ = kv_pool.shape
-    if (two, nkv_, hd_) != (2, nkv, hd) or not kv_pool.is_contiguous():
-        raise KernelError(f"attention: kv_pool is {tuple(kv_pool.shape)}, expected [pages, 2, {nkv}, page, {hd}]")
-    if out.stride(1) != 1 or out.shape[1] < nh * hd or out.shape[0] < n_rows:
-        raise KernelError("attention: out must be [T, nh*hd] with unit inner stride")
+    vd = hd if vd is None else int(vd)
+    if vd == hd:
+        num_pages, two, nkv_, page_size, hd_ = kv_pool.shape
+        if (two, nkv_, hd_) != (2, nkv, hd) or not kv_pool.is_contiguous():
+            raise KernelError(f"attention: kv_pool is {tuple(kv_pool.shape)}, expected [pages, 2, {nkv}, page, {hd}]")
+    else:
+        # values of another size than keys: a page is flat, the keys of all kv heads followed by their values
+        if kernel != "generic":
+            raise KernelError("attention: values of another size than keys run the CUDA-core kernel")
+        if kv_pool.dim() != 2 or kv_pool.shape[1] % (nkv * (hd + vd)) or not kv_pool.is_contiguous():
+            raise KernelError(f"attention: kv_pool is {tuple(kv_pool.shape)}, expected [pages, {nkv} * page * ({hd} + {vd})]")
+        num_pages, page_size = kv_pool.shape[0], kv_pool.shape[1] // (nkv * (hd + vd))
+    if sink and kernel not in SINK_KERNELS:
+        raise KernelError(f"attention: the kernel '{kernel}' has no softmax with an enlarged denominator")
+    if out.stride(1) != 1 or out.shape[1] < nh * vd or out.shape[0] < n_rows:
+        raise KernelError("attention: out must be [T, nh*vd] with unit inner stride")
     L = lib()
     if kernel == "tc_rows":
         if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
@@ -548,12 +586,12 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
             return
     else:
         n_splits = max_position // split + 1
-    part_o = torch.empty((n_rows * nh * n_splits, hd), dtype=torch.float32, device=q.device)
+    part_o = torch.empty((n_rows * nh * n_splits, vd), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((n_rows * nh * n_splits, 2), dtype=torch.float32, device=q.device)
     if kernel == "generic":
         _check(L.bg_attention_partial(_p(q), _dt(q), q_stride, _p(kv_pool), _dt(kv_pool), num_pages, page_size,
                                       _p(block_table), block_table.shape[1], _p(positions), _p(qblk), n_qblk,
-                                      _p(part_o), _p(part_ml), n_splits, n_splits, nh, nkv, hd, window, split, tile,
+                                      _p(part_o), _p(part_ml), n_splits, n_splits, nh, nkv, hd, vd, window, split, tile,
                                       bq, float(scale), _p(status), _stream()), "attention_partial")
     elif kernel == "mma_keys":
         if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16:
@@ -566,7 +604,7 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
     else:
         raise KernelError(f"unknown attention kernel '{kernel}'")
     _check(L.bg_attention_merge(_p(part_o), _p(part_ml), _p(positions), _p(out), _dt(out), out.stride(0), n_rows, nh,
-                                hd, n_splits, split, window, _stream()), "attention_merge")
+                                vd, n_splits, split, window, 1 if sink else 0, _stream()), "attention_merge")
 
 
 def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
@@ -1134,3 +1172,165 @@ def gated_group_rmsnorm(y: torch.Tensor, src: torch.Tensor, z_col: int, weight: 
     with phase("rmsnorm"):
         _check(lib().bg_gated_group_rmsnorm(_p(y), _p(src), _dt(src), src.stride(0), z_col, _p(weight), _dt(weight), float(eps),
                                             _p(out), _dt(out), T, inner, groups, _stream()), "gated_group_rmsnorm")
+
+
+def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, lowp: Optional[torch.Tensor] = None) -> None:
+    """x += rmsnorm(y) * weight for y [T, d] or its float partial sums [parts, T, d]; statistics and sum in float.
+    `lowp`, when given, receives the new rows of x rounded to its type."""
+    _cuda(x, y, weight, lowp)
+    T, d = x.shape
+    parts, stride = _parts(y, "rmsnorm_add: y")
+    if x.dtype != torch.float32 or not x.is_contiguous() or tuple(y.shape[-2:]) != (T, d) or not y.is_contiguous():
+        raise KernelError("rmsnorm_add: x contiguous float32 [T, d], y shaped like it (or its partial sums)")
+    if parts > 1 and y.dtype != torch.float32:
+        raise KernelError("rmsnorm_add: partial sums are float32")
+    if weight.numel() != d or not weight.is_contiguous():
+        raise KernelError(f"rmsnorm_add: weight has {weight.numel()} of {d} values")
+    if lowp is not None and (tuple(lowp.shape) != (T, d) or not lowp.is_contiguous()):
+        raise KernelError("rmsnorm_add: lowp must be contiguous and shaped like x")
+    with phase("rmsnorm"):
+        _check(lib().bg_rmsnorm_add(_p(x), _p(y), _dt(y), parts, stride, _p(weight), _dt(weight), float(eps), _p(lowp),
+                                    _dt(lowp) if lowp is not None else F32, T, d, _stream()), "rmsnorm_add")
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x rounded to out's type (x float32)."""
+    _cuda(x, out)
+    if x.dtype != torch.float32 or x.shape != out.shape or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("cast_rows: x contiguous float32, out contiguous and shaped like it")
+    with phase("residuals"):
+        _check(lib().bg_cast_rows(_p(x), _p(out), _dt(out), x.numel(), _stream()), "cast_rows")
+
+
+def qk_norm_rope_append(src: torch.Tensor, q_out: torch.Tensor, n_rows: int, nh: int, nkv: int, hd: int, vd: int, rot: int,
+                        interleaved: bool, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                        cos_sin: Optional[torch.Tensor], positions: torch.Tensor, row_req: torch.Tensor,
+                        block_table: torch.Tensor, kv_pool: Optional[torch.Tensor], page_size: int,
+                        status: Optional[torch.Tensor]) -> None:
+    """Rows [q | k | v | ...] of `src` ([T, W], or float partial sums [parts, T, W]): RMS norm of the whole q row and of
+    the whole k row with the float weights given (None: no norm), rotation of the first `rot` features of every head,
+    q into q_out [T, nh*hd], k and v into the paged cache (a page: keys [nkv, page, hd], then values [nkv, page, vd])."""
+    _cuda(src, q_out, q_weight, k_weight, cos_sin, positions, row_req, block_table, kv_pool)
+    _i32(positions, "positions"); _i32(row_req, "row_req"); _i32(block_table, "block_table")
+    parts, stride = _parts(src, "qk_norm_rope_append: src")
+    need = nh * hd + (nkv * (hd + vd) if kv_pool is not None else 0)
+    if src.stride(-1) != 1 or src.shape[-1] < need or src.shape[-2] < n_rows:
+        raise KernelError(f"qk_norm_rope_append: rows of {src.shape[-1]} features cannot hold q, k, v ({need})")
+    if q_out.stride(1) != 1 or q_out.shape[1] < nh * hd or q_out.shape[0] < n_rows:
+        raise KernelError("qk_norm_rope_append: q_out must be [T, nh*hd]")
+    for w, n in ((q_weight, nh * hd), (k_weight, nkv * hd)):
+        if w is not None and (w.dtype != torch.float32 or w.numel() != n or not w.is_contiguous()):
+            raise KernelError("qk_norm_rope_append: norm weights are contiguous float32 of the projection's width")
+    num_pages = 0
+    if kv_pool is not None:
+        if not kv_pool.is_contiguous() or kv_pool[0].numel() != nkv * page_size * (hd + vd):
+            raise KernelError(f"qk_norm_rope_append: a page of {tuple(kv_pool.shape)} does not hold {nkv} x {page_size} x ({hd} + {vd})")
+        num_pages = kv_pool.shape[0]
+    if rot > 0 and (cos_sin is None or cos_sin.shape[0] < n_rows or cos_sin.shape[1] != rot // 2 or cos_sin.dtype != torch.float32):
+        raise KernelError("qk_norm_rope_append: cos_sin must be float32 [T, rot/2, 2]")
+    with phase("rope+kv_write"):
+        _check(lib().bg_qk_norm_rope_append(_p(src), _dt(src), src.stride(-2), parts, stride, _p(q_out), _dt(q_out), q_out.stride(0),
+                                            _p(q_weight), _p(k_weight), float(eps), _p(cos_sin), _p(positions), _p(row_req),
+                                            _p(block_table), block_table.shape[1], _p(kv_pool),
+                                            _dt(kv_pool) if kv_pool is not None else _dt(q_out), num_pages, page_size, n_rows, nh,
+                                            nkv, hd, vd, rot, 1 if interleaved else 0, _p(status), _stream()),
+               "qk_norm_rope_append")
+
+
+def sigmoid_gate(out: torch.Tensor, gate: torch.Tensor, col0: int, n: int) -> None:
+    """out[t, j] *= sigmoid(gate[t, col0 + j]) for j < n; gate is [T, W] or its float partial sums [parts, T, W]."""
+    _cuda(out, gate)
+    parts, stride = _parts(gate, "sigmoid_gate: gate")
+    T = out.shape[0]
+    if out.dim() != 2 or out.stride(1) != 1 or out.shape[1] < n or gate.stride(-1) != 1 or gate.shape[-2] < T or col0 + n > gate.shape[-1]:
+        raise KernelError("sigmoid_gate: out [T, >= n], gate rows that hold n values from col0")
+    with phase("activation"):
+        _check(lib().bg_sigmoid_gate(_p(out), _dt(out), out.stride(0), _p(gate), _dt(gate), gate.stride(-2), parts, stride, col0, T, n,
+                                     _stream()), "sigmoid_gate")
+
+
+# ---------------------------------------------------------------------------------------------------- routed experts
+EXPERT_ACTIVATIONS = {"none": 0, "relu2": 1}
+
+
+def route_logits(h: torch.Tensor, router: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, e] = sum_k h[t, k] router[e, k], float: h in either type, router and out float32.  CUDA cores."""
+    _cuda(h, router, out)
+    T, d = h.shape
+    E = router.shape[0]
+    if router.dtype != torch.float32 or out.dtype != torch.float32 or router.shape[1] != d or tuple(out.shape) != (T, E) \
+            or h.stride(1) != 1 or not router.is_contiguous() or not out.is_contiguous():
+        raise KernelError("route_logits: h [T, d], router float32 [E, d], out float32 [T, E]")
+    with phase("router"):
+        _check(lib().bg_route_logits(_p(h), _dt(h), h.stride(0), _p(router), d, _p(out), E, T, E, d, _stream()), "route_logits")
+
+
+def route_topk(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor, sigmoid: bool = True,
+               renorm: bool = False) -> None:
+    """Per row of float logits [T, E]: the `top` experts of largest score into ids [T, top] (int32) and their scores
+    into weights [T, top] (float32)."""
+    _cuda(logits, ids, weights)
+    T, E = logits.shape
+    _i32(ids, "ids")
+    if logits.dtype != torch.float32 or weights.dtype != torch.float32 or not logits.is_contiguous() \
+            or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top) or not ids.is_contiguous() or not weights.is_contiguous():
+        raise KernelError("route_topk: logits float32 [T, E], ids int32 [T, top], weights float32 [T, top]")
+    with phase("router"):
+        _check(lib().bg_route_topk(_p(logits), T, E, top, 1 if sigmoid else 0, 1 if renorm else 0, _p(ids), _p(weights), _stream()),
+               "route_topk")
+
+
+def route_sort(ids: torch.Tensor, E: int, offsets: torch.Tensor, row_of: torch.Tensor, src_of: torch.Tensor) -> None:
+    """The assignments ids [A] laid out expert by expert: offsets int32 [E + 1], row_of [A] (where each went), src_of [A]."""
+    _cuda(ids, offsets, row_of, src_of)
+    for t, n in ((ids, "ids"), (offsets, "offsets"), (row_of, "row_of"), (src_of, "src_of")):
+        _i32(t, n)
+    A = ids.numel()
+    if offsets.numel() != E + 1 or row_of.numel() != A or src_of.numel() != A:
+        raise KernelError("route_sort: offsets [E + 1], row_of and src_of [A]")
+    with phase("router"):
+        _check(lib().bg_route_sort(_p(ids), A, E, _p(offsets), _p(row_of), _p(src_of), _stream()), "route_sort")
+
+
+def route_gather(x: torch.Tensor, weights: torch.Tensor, src_of: torch.Tensor, out: torch.Tensor, top: int, scale: bool) -> None:
+    """out[row] = (weights[a] *) x[a // top] for a = src_of[row], rounded to out's type."""
+    _cuda(x, weights, src_of, out)
+    A, d = out.shape
+    if not x.is_contiguous() or not out.is_contiguous() or x.shape[1] != d or weights.numel() != A or src_of.numel() != A:
+        raise KernelError("route_gather: x [T, d], out [T * top, d], weights and src_of [T * top]")
+    with phase("router"):
+        _check(lib().bg_route_gather(_p(x), _dt(x), _p(weights), _p(src_of), _p(out), _dt(out), A, d, top, 1 if scale else 0,
+                                     _stream()), "route_gather")
+
+
+def route_combine(yp: torch.Tensor, weights: torch.Tensor, row_of: torch.Tensor, out: torch.Tensor, top: int, scale: bool) -> None:
+    """out[t] = sum over j < top of (weights[t * top + j] *) yp[row_of[t * top + j]], ranks in index order, float."""
+    _cuda(yp, weights, row_of, out)
+    T, d = out.shape
+    if out.dtype != torch.float32 or not yp.is_contiguous() or not out.is_contiguous() or tuple(yp.shape) != (T * top, d):
+        raise KernelError("route_combine: yp [T * top, d], out float32 [T, d]")
+    with phase("router"):
+        _check(lib().bg_route_combine(_p(yp), _dt(yp), _p(weights), _p(row_of), _p(out), T, d, top, 1 if scale else 0, _stream()),
+               "route_combine")
+
+
+def gemm_grouped(x: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, out: torch.Tensor, activation: str = "none",
+                 status: Optional[torch.Tensor] = None, tensor_cores: bool = True) -> None:
+    """out[row] = act(x[row] w[e]^T) for the rows offsets[e] .. offsets[e + 1] of every expert e: x [A, K], w [E, N, K],
+    out [A, N].  bfloat16 operands whose K is a multiple of 8 run the tcgen05 kernel (unless `tensor_cores` is False);
+    float32 operands, and every other size, the CUDA-core kernel."""
+    _cuda(x, w, offsets, out)
+    _i32(offsets, "offsets")
+    A, K = x.shape
+    E, N, K2 = w.shape
+    if K2 != K or tuple(out.shape) != (A, N) or offsets.numel() != E + 1 or x.dtype != w.dtype \
+            or not x.is_contiguous() or not w.is_contiguous() or not out.is_contiguous():
+        raise KernelError("gemm_grouped: x [A, K], w [E, N, K] of x's type, out [A, N], offsets [E + 1], all contiguous")
+    act = EXPERT_ACTIVATIONS[activation]
+    with phase("experts"):
+        if tensor_cores and x.dtype == torch.bfloat16 and K % 8 == 0:
+            _check(lib().bg_gemm_grouped_tc(_p(w), E, N, K, K, _p(x), A, K, _p(out), _dt(out), N, _p(offsets), act, _p(status),
+                                            _stream()), "gemm_grouped_tc")
+        else:
+            _check(lib().bg_gemm_grouped(_p(x), _dt(x), K, _p(w), K, N * K, _p(out), _dt(out), N, _p(offsets), E, A, N, K, act,
+                                         _stream()), "gemm_grouped")

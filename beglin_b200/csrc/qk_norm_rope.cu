@@ -1,0 +1,162 @@
+// What stands between the q/k/v product and the attention for a mixer whose queries and keys are normed over the
+// WHOLE projection and whose values may be narrower than its keys: for every token of a step
+//   q <- q * rsqrt(mean over all heads' features of q^2 + eps) * wq      (likewise k with wk; skipped without weights)
+//   the leading `rot` features of every head of q and k turn by the token's angles (pairs (i, i + rot/2), or
+//   (2i, 2i + 1) when interleaved); the rest pass unchanged
+//   q goes to q_out [T, nh*hd]; k and v go to the token's place in the paged cache.
+// A page holds the keys of all kv heads, [nkv][page_size][hd], followed by their values, [nkv][page_size][vd]; with
+// vd == hd that is the layout [2][nkv][page_size][hd] of the other attention kernels.
+// The source rows are [q | k | v | ...] as the product left them (any trailing columns are ignored), or the float
+// partial sums of a split-K product, added in index order.  Statistics, scaling and rotation are float; a value is
+// rounded once, when it is stored.  One block per token, its q and k held in shared memory.
+#include "common.cuh"
+
+namespace bg {
+
+struct QkNormRopeParams {
+    const void* src; int src_stride; int parts; size_t part_stride;
+    void* q_out; int q_stride;
+    const float* wq; const float* wk; float eps;            // null: no norm
+    const float* cos_sin;                                    // [T][rot/2][2] or null when rot == 0
+    const int* positions; const int* row_req; const int* block_table; int max_pages;
+    void* pool; int num_pages, page_size;                    // null pool: the rows hold queries only
+    int nh, nkv, hd, vd, rot, interleaved;
+    unsigned* status;
+};
+
+template <typename TS, typename TQ, typename TC>
+__global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(QkNormRopeParams p) {
+    extern __shared__ float qk_s[];                          // [nh*hd] queries, then [nkv*hd] keys
+    __shared__ float red[32];
+    pdl_launch();
+    const int t = blockIdx.x;
+    const int qd = p.nh * p.hd, kd = p.pool ? p.nkv * p.hd : 0, vdd = p.pool ? p.nkv * p.vd : 0;
+    const int half = p.rot / 2;
+    const TS* row = (const TS*)p.src + (size_t)t * p.src_stride;
+    // the token's place depends on no kernel of the step
+    const int pos = p.positions[t];
+    long long k_base = -1, v_base = -1;
+    if (p.pool) {
+        const int req = p.row_req[t];
+        const int page = p.block_table[(size_t)req * p.max_pages + pos / p.page_size];
+        if (page < 0 || page >= p.num_pages) {
+            if (p.status && threadIdx.x == 0) atomicOr(p.status, BG_STATUS_BAD_PAGE);
+        } else {
+            const size_t page_elems = (size_t)p.nkv * p.page_size * (p.hd + p.vd);
+            const int slot = pos % p.page_size;
+            k_base = (long long)((size_t)page * page_elems + (size_t)slot * p.hd);
+            v_base = (long long)((size_t)page * page_elems + (size_t)p.nkv * p.page_size * p.hd + (size_t)slot * p.vd);
+        }
+    }
+    pdl_wait();
+    float ssq = 0.0f, ssk = 0.0f;
+    for (int i = threadIdx.x; i < qd + kd; i += blockDim.x) {
+        const float v = sum_parts(row + i, p.parts, p.part_stride);
+        qk_s[i] = v;
+        if (i < qd) ssq += v * v; else ssk += v * v;
+    }
+    if (p.wq) {
+        ssq = block_sum(ssq, red);
+        ssk = block_sum(ssk, red);
+        const float inv_q = 1.0f / sqrtf(ssq / (float)qd + p.eps);
+        const float inv_k = kd > 0 ? 1.0f / sqrtf(ssk / (float)kd + p.eps) : 0.0f;
+        __syncthreads();
+        for (int i = threadIdx.x; i < qd + kd; i += blockDim.x)
+            qk_s[i] = i < qd ? qk_s[i] * inv_q * p.wq[i] : qk_s[i] * inv_k * p.wk[i - qd];
+    }
+    __syncthreads();
+    const float* cs = p.cos_sin ? p.cos_sin + (size_t)t * half * 2 : nullptr;
+    TQ* qo = (TQ*)p.q_out + (size_t)t * p.q_stride;
+    TC* pool = (TC*)p.pool;
+    for (int i = threadIdx.x; i < qd + kd; i += blockDim.x) {
+        const int j = i < qd ? i : i - qd;
+        const int h = j / p.hd, f = j - h * p.hd;
+        float v = qk_s[i];
+        if (f < p.rot) {
+            int pair, partner;
+            bool low;
+            if (p.interleaved) { pair = f >> 1; low = (f & 1) == 0; partner = low ? i + 1 : i - 1; }
+            else { low = f < half; pair = low ? f : f - half; partner = low ? i + half : i - half; }
+            const float c = cs[2 * pair], s = cs[2 * pair + 1], o = qk_s[partner];
+            v = low ? v * c - o * s : v * c + o * s;
+        }
+        if (i < qd) qo[j] = from_float<TQ>(v);
+        else if (k_base >= 0) pool[k_base + (size_t)h * p.page_size * p.hd + f] = from_float<TC>(v);
+    }
+    if (v_base >= 0) {
+        for (int i = threadIdx.x; i < vdd; i += blockDim.x) {
+            const int h = i / p.vd, f = i - h * p.vd;
+            pool[v_base + (size_t)h * p.page_size * p.vd + f] = from_float<TC>(sum_parts(row + qd + kd + i, p.parts, p.part_stride));
+        }
+    }
+}
+
+// out[t][j] *= sigmoid(gate[t][col0 + j]) for j < n: the gate is a column range of a wider row (or of its partial sums).
+template <typename TG, typename TO>
+__global__ void sigmoid_gate_kernel(TO* __restrict__ out, int out_stride, const TG* __restrict__ gate, int gate_stride, int parts,
+                                    size_t part_stride, int col0, int rows, int n) {
+    pdl_launch();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool idle = idx >= (size_t)rows * n;
+    const size_t t = idle ? 0 : idx / n;
+    const int j = idle ? 0 : (int)(idx - t * n);
+    pdl_wait();
+    if (idle) return;
+    const float g = sum_parts(gate + t * gate_stride + col0 + j, parts, part_stride);
+    TO* o = out + t * out_stride + j;
+    *o = from_float<TO>(to_float(*o) / (1.0f + expf(-g)));
+}
+
+}  // namespace bg
+
+using namespace bg;
+
+template <typename TS, typename TQ, typename TC>
+static int qk_norm_rope_launch(const QkNormRopeParams& p, int T, cudaStream_t stream) {
+    auto kern = qk_norm_rope_append_kernel<TS, TQ, TC>;
+    const size_t smem = (size_t)(p.nh * p.hd + (p.pool ? p.nkv * p.hd : 0)) * sizeof(float);
+    if (smem > 200 * 1024) return BG_ERR_SHAPE;
+    if (smem > BG_SMEM_OPT_IN) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    launch(kern, dim3(T), dim3(256), smem, stream, p);
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_qk_norm_rope_append(const void* src, int src_dtype, int src_stride, int parts, long long part_stride,
+                                      void* q_out, int q_dtype, int q_stride, const float* wq, const float* wk, float eps,
+                                      const float* cos_sin, const int* positions, const int* row_req, const int* block_table,
+                                      int max_pages, void* pool, int cache_dtype, int num_pages, int page_size, int T, int nh,
+                                      int nkv, int hd, int vd, int rot, int interleaved, unsigned* status, cudaStream_t stream) {
+    if (T <= 0) return BG_OK;
+    if (rot < 0 || rot > hd || rot % 2 || parts < 1 || (rot > 0 && !cos_sin) || ((wq == nullptr) != (wk == nullptr))) return BG_ERR_SHAPE;
+    if (src_dtype != q_dtype && src_dtype != BG_DTYPE_F32) return BG_ERR_DTYPE;
+    QkNormRopeParams p;
+    p.src = src; p.src_stride = src_stride; p.parts = parts; p.part_stride = (size_t)part_stride; p.q_out = q_out;
+    p.q_stride = q_stride; p.wq = wq; p.wk = wk; p.eps = eps; p.cos_sin = cos_sin; p.positions = positions; p.row_req = row_req;
+    p.block_table = block_table; p.max_pages = max_pages; p.pool = pool; p.num_pages = num_pages; p.page_size = page_size;
+    p.nh = nh; p.nkv = nkv; p.hd = hd; p.vd = vd; p.rot = rot; p.interleaved = interleaved; p.status = status;
+    if (!pool) cache_dtype = q_dtype;
+    if (cache_dtype != q_dtype) return BG_ERR_DTYPE;            // queries and cache are both of the compute type
+    if (q_dtype == BG_DTYPE_F32) {
+        if (src_dtype != BG_DTYPE_F32) return BG_ERR_DTYPE;
+        return qk_norm_rope_launch<float, float, float>(p, T, stream);
+    }
+    if (src_dtype == BG_DTYPE_F32) return qk_norm_rope_launch<float, __nv_bfloat16, __nv_bfloat16>(p, T, stream);
+    return qk_norm_rope_launch<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(p, T, stream);
+}
+
+extern "C" int bg_sigmoid_gate(void* out, int out_dtype, int out_stride, const void* gate, int gate_dtype, int gate_stride,
+                               int parts, long long part_stride, int col0, int rows, int n, cudaStream_t stream) {
+    if (rows <= 0 || n <= 0) return BG_OK;
+    if (parts < 1) return BG_ERR_SHAPE;
+    const size_t total = (size_t)rows * n;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    BG_DISPATCH_DTYPE(gate_dtype, TG, BG_DISPATCH_DTYPE(out_dtype, TO,
+        launch(sigmoid_gate_kernel<TG, TO>, dim3(blocks), dim3(256), 0, stream, (TO*)out, out_stride, (const TG*)gate, gate_stride,
+               parts, (size_t)part_stride, col0, rows, n)));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}

@@ -6,6 +6,12 @@ their biases at load time too, qwen_infer.c:1316-1367), rotation of q and k fuse
 of k and v to the pages, attention of every row over the pages of its own request, and the output
 product.  All rows' keys and values are in the cache before any row's attention runs
 (qwen_infer.c:2017-2023), which is what makes a prompt portion causal.
+
+Options of the spec, each off for the plain form: values of another size than keys; an RMS norm of the whole query
+row and of the whole key row of a token before the rotation; a softmax whose denominator is enlarged by one; a gate,
+sigmoid of a further product of the mixer's input, on the joined heads before the output product.  The gate's matrix is
+one more block of rows of the one q/k/v product.  With any of the first two the kernel that norms, rotates and appends
+is `qk_norm_rope_append`.
 """
 from __future__ import annotations
 
@@ -30,24 +36,32 @@ class GQAAttention:
     @staticmethod
     def expected_tensors(spec: AttentionSpec) -> List[TensorRole]:
         qd, kvd = spec.n_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
+        vvd, od = spec.n_kv_heads * spec.value_dim, spec.n_heads * spec.value_dim
         roles = [TensorRole("q_proj.weight", (qd, spec.hidden), True, True),
-                 TensorRole("o_proj.weight", (spec.hidden, qd), True, True)]
+                 TensorRole("o_proj.weight", (spec.hidden, od), True, True)]
         if spec.own_kv:
             roles += [TensorRole("k_proj.weight", (kvd, spec.hidden), True, True),
-                      TensorRole("v_proj.weight", (kvd, spec.hidden), True, True)]
+                      TensorRole("v_proj.weight", (vvd, spec.hidden), True, True)]
         if spec.qkv_bias:
             roles.append(TensorRole("q_proj.bias", (qd,), role="bias"))
             if spec.own_kv:
-                roles += [TensorRole("k_proj.bias", (kvd,), role="bias"), TensorRole("v_proj.bias", (kvd,), role="bias")]
+                roles += [TensorRole("k_proj.bias", (kvd,), role="bias"), TensorRole("v_proj.bias", (vvd,), role="bias")]
         if spec.out_bias:
             roles.append(TensorRole("o_proj.bias", (spec.hidden,), role="bias"))
+        if spec.qk_norm is not None:
+            roles.append(TensorRole("q_norm.weight", (qd,), role="scale"))
+            if spec.own_kv:
+                roles.append(TensorRole("k_norm.weight", (kvd,), role="scale"))
+        if spec.gate is not None:
+            roles.append(TensorRole("g_proj.weight", (od, spec.hidden), True, True))
         return roles
 
     @staticmethod
     def cache_need(spec: AttentionSpec) -> Optional[PagedKVNeed]:
         if not spec.own_kv:
             return None
-        return PagedKVNeed(spec.n_kv_heads, spec.head_dim, spec.window)
+        return PagedKVNeed(spec.n_kv_heads, spec.head_dim, spec.window,
+                           None if spec.value_dim == spec.head_dim else spec.value_dim)
 
     def __init__(self, spec: AttentionSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
         if spec.n_heads % spec.n_kv_heads:
@@ -55,24 +69,42 @@ class GQAAttention:
         if spec.head_dim % 2 or spec.head_dim > 256:
             raise ValueError(f"head_dim={spec.head_dim} must be even and at most 256")
         self.spec, self.ctx = spec, ctx
-        self.nh, self.nkv, self.hd = spec.n_heads, spec.n_kv_heads, spec.head_dim
+        if spec.qk_norm not in (None, "projection"):
+            raise ValueError(f"unknown query/key norm '{spec.qk_norm}' (projection)")
+        if spec.gate not in (None, "elementwise"):
+            raise ValueError(f"unknown output gate '{spec.gate}' (elementwise)")
+        self.nh, self.nkv, self.hd, self.vd = spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.value_dim
+        if self.vd <= 0 or self.vd > 256:
+            raise ValueError(f"v_head_dim={self.vd} must be positive and at most 256")
         self.qd, self.kvd = self.nh * self.hd, self.nkv * self.hd
+        self.od = self.nh * self.vd
+        # what the plain form does not have: the step between product and attention is then a kernel of its own
+        self.extended = spec.qk_norm is not None or self.vd != self.hd or spec.gate is not None
+        if self.extended and (spec.qkv_bias and spec.gate is not None or not spec.own_kv):
+            raise ValueError("the extended attention has a cache of its own and no bias beside a gate")
         names = ["q_proj"] + (["k_proj", "v_proj"] if spec.own_kv else [])
-        w = torch.cat([tensors[n + ".weight"] for n in names], dim=0)
+        w = torch.cat([tensors[n + ".weight"] for n in names] + ([tensors["g_proj.weight"]] if spec.gate else []), dim=0)
         b = torch.cat([tensors[n + ".bias"].float() for n in names], dim=0) if spec.qkv_bias else None
+        self.gate_col = self.qd + (self.kvd + self.nkv * self.vd if spec.own_kv else 0)
+        f32 = lambda t: t.to(device=ctx.device, dtype=torch.float32).contiguous()
+        self.q_norm = f32(tensors["q_norm.weight"]) if spec.qk_norm else None
+        self.k_norm = f32(tensors["k_norm.weight"]) if spec.qk_norm else None
         self.qkv = Linear(w, b, ctx, label="proj_qkv")
         self.o_proj = Linear(tensors["o_proj.weight"], tensors.get("o_proj.bias") if spec.out_bias else None, ctx,
                              label="proj_o")
         self.position = shared_position(spec.position, ctx)
         scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(float(self.hd))
         self.scale = float(np.float32(scale))
-        self.plans = {d: ops.attention_plan(self.nh // self.nkv, self.hd, ctx.cache_dtype, d, ctx.attention,
-                                            ctx.page_size) for d in (False, True)}
+        # (a softmax with the enlarged denominator runs the kernels that have it)
+        prefer = ctx.attention if not spec.sink or ctx.attention in ops.SINK_KERNELS else "generic"
+        self.plans = {d: ops.attention_plan(self.nh // self.nkv, self.hd, ctx.cache_dtype, d, prefer,
+                                            ctx.page_size, vd=self.vd) for d in (False, True)}
         self.window = int(spec.window) if spec.window else 0
         # the fused q/k/v product can rotate and append itself: whole heads rotated in halves, a cache of its own
         # in bfloat16
         self.rope_in_product = (spec.own_kv and self.position.rotary_dim == self.hd and not self.position.interleaved
-                                and ctx.compute_dtype == torch.bfloat16 and ctx.cache_dtype == torch.bfloat16)
+                                and ctx.compute_dtype == torch.bfloat16 and ctx.cache_dtype == torch.bfloat16
+                                and not self.extended)
 
     takes_stream = True        # forward takes a NormedInput and may add its result to the stream itself
 
@@ -80,7 +112,15 @@ class GQAAttention:
         """h: the normed rows, or a NormedInput.  With `stream` the result is added to it (or left owed to
         it) and None is returned; without, the addend is returned."""
         T = batch.n_rows
-        if self.rope_in_product and self.qkv.rope_fuses(T, self.hd):
+        qkv = None
+        if self.extended:
+            qkv = self.qkv.of(h)
+            q = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=qkv.device)
+            ops.qk_norm_rope_append(qkv, q, T, self.nh, self.nkv, self.hd, self.vd, self.position.rotary_dim,
+                                    self.position.interleaved, self.q_norm, self.k_norm, self.spec.qk_norm_eps,
+                                    self.position.table(batch), batch.positions, batch.row_req, cache.block_table,
+                                    cache.pool, cache.page_size, self.ctx.status)
+        elif self.rope_in_product and self.qkv.rope_fuses(T, self.hd):
             # a step of few tokens: rotation and cache append inside the q/k/v product
             q = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=self.ctx.device)
             self.qkv.of_rope(h, q, (self.position.table(batch), batch.positions, batch.row_req, cache.block_table,
@@ -96,10 +136,12 @@ class GQAAttention:
         if qblk is None and kernel != "mma_keys":
             batch.implicit_blocks = False              # this kernel wants the list
             qblk, n_qblk = batch.query_blocks(bq)
-        out = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=q.device)
+        out = torch.empty((T, self.od), dtype=self.ctx.compute_dtype, device=q.device)
         ops.attention(q, q.stride(0), cache.pool, cache.block_table, batch.positions, qblk, n_qblk,
                       batch.max_position, T, self.nh, self.nkv, self.hd, self.window, self.ctx.kv_split, tile, bq,
-                      self.scale, out, self.ctx.status, kernel)
+                      self.scale, out, self.ctx.status, kernel, vd=self.vd, sink=self.spec.sink)
+        if self.spec.gate is not None:
+            ops.sigmoid_gate(out, qkv, self.gate_col, self.od)
         if stream is None:
             return self.o_proj.partial(out)
         self.o_proj.into(out, stream)

@@ -7,6 +7,9 @@ stream.py).  The other kinds are the same layer without a feed-forward, and eith
 behind it: a part that rewrites the stream from the results of this and earlier layers."""
 from __future__ import annotations
 
+import torch
+
+from ..csrc import ops
 from .registry import register_block
 from .stream import NormedInput, ResidualStream
 
@@ -63,3 +66,43 @@ class PreNormCombinedBlock(PreNormBlock):
 @register_block("prenorm_mixer_combined")
 class PreNormMixerCombinedBlock(PreNormBlock):
     SLOTS = PreNormMixerBlock.SLOTS + (("combiner", "combiner"),)
+
+
+@register_block("postnorm")
+class PostNormBlock:
+    """The norm stands on a sublayer's RESULT, not on its input: x += norm(mixer(x)), then x += norm(feed_forward(x)).
+    The sublayers read the stream as it is: the float rows themselves in the float32 path, their rounding to the
+    compute type otherwise (left behind by the kernel that last added to the stream, so no kernel runs for it
+    except before a model's first layer).  The statistics of the norm and the sum are float."""
+    SLOTS = (("mixer", "mixer"), ("mixer_norm", "norm"), ("feed_forward", "feed_forward"), ("feed_forward_norm", "norm"))
+
+    def __init__(self, mixer, mixer_norm, feed_forward=None, feed_forward_norm=None):
+        self.mixer, self.mixer_norm = mixer, mixer_norm
+        self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
+
+    @staticmethod
+    def rows(stream: ResidualStream, dtype: torch.dtype) -> torch.Tensor:
+        """The stream's rows in the compute type."""
+        if stream.pending is not None:                 # something an earlier block of another kind still owes
+            ops.add_residual(stream.x, stream.pending)
+            stream.updated(None)
+        if dtype == torch.float32:
+            return stream.x
+        if stream.lowp is None:
+            stream.lowp = torch.empty(stream.x.shape, dtype=dtype, device=stream.x.device)
+            ops.cast_rows(stream.x, stream.lowp)
+        return stream.lowp
+
+    def forward(self, stream: ResidualStream, batch, cache) -> None:
+        dtype = self.mixer_norm.ctx.compute_dtype
+        a = self.mixer.forward(self.rows(stream, dtype), batch, cache)
+        stream.updated(None, self.mixer_norm.norm_add(stream.x, a, want_lowp=True))
+        if self.feed_forward is not None:
+            m = self.feed_forward.forward(self.rows(stream, dtype), batch)
+            stream.updated(None, self.feed_forward_norm.norm_add(stream.x, m, want_lowp=True))
+
+
+@register_block("postnorm_mixer")
+class PostNormMixerBlock(PostNormBlock):
+    """The same layer without a feed-forward."""
+    SLOTS = (("mixer", "mixer"), ("mixer_norm", "norm"))

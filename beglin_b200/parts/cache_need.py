@@ -14,14 +14,20 @@ import torch
 
 @dataclass(frozen=True)
 class PagedKVNeed:
-    """Keys and values of every position (window None) or of the last `window` positions."""
+    """Keys and values of every position (window None) or of the last `window` positions.  `v_head_dim` is given
+    when values have another size than keys."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
-        """What one page of one stage holds: (2 = keys, values; kv heads; positions; features)."""
-        return (2, self.n_kv_heads, page_size, self.head_dim)
+        """What one page of one stage holds: (2 = keys, values; kv heads; positions; features); with values of
+        another size than keys, flat: the keys (kv heads; positions; head_dim) followed by the values (kv heads;
+        positions; v_head_dim)."""
+        if self.v_head_dim is None or self.v_head_dim == self.head_dim:
+            return (2, self.n_kv_heads, page_size, self.head_dim)
+        return (self.n_kv_heads * page_size * (self.head_dim + self.v_head_dim),)
 
 
 @dataclass(frozen=True)

@@ -33,6 +33,16 @@ class RMSNorm:
         ops.add_rmsnorm(x, delta, self.weight, self.spec.eps, out, rows=rows, update=update and rows is None)
         return out
 
+    def norm_add(self, x: torch.Tensor, y: torch.Tensor, want_lowp: bool = False) -> Optional[torch.Tensor]:
+        """The norm on a sublayer's RESULT: x += norm(y) * weight, for y [T, size] or its float partial sums
+        [parts, T, size]; statistics and sum in float.  With `want_lowp` the new rows of x are also returned in
+        the compute type (for the next sublayer, which reads the stream as it is)."""
+        lowp = None
+        if want_lowp and self.ctx.compute_dtype != torch.float32:
+            lowp = torch.empty(x.shape, dtype=self.ctx.compute_dtype, device=x.device)
+        ops.rmsnorm_add(x, y, self.weight, self.spec.eps, lowp)
+        return lowp
+
     def fusion(self):
         """What a product needs to apply this norm to its operand itself: (weight, eps); None when the
         weight is not in the compute type (a checkpoint that stores it in 32-bit keeps it so)."""

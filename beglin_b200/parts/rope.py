@@ -30,6 +30,12 @@ class RotaryPosition:
         half = spec.rotary_dim // 2
         exponent = -(np.float32(2.0) * np.arange(half, dtype=np.float32)) / np.float32(spec.rotary_dim)
         inv = np.power(np.float64(np.float32(spec.theta)), exponent.astype(np.float64)).astype(np.float32)
+        if spec.freq_divisor is not None:
+            # frequencies divided by a constant: worked out in 64-bit from the exact exponents and rounded once
+            if not spec.freq_divisor > 0.0:
+                raise ValueError(f"freq_divisor={spec.freq_divisor} must be positive")
+            exact = np.power(np.float64(spec.theta), -2.0 * np.arange(half, dtype=np.float64) / np.float64(spec.rotary_dim))
+            inv = (exact / np.float64(spec.freq_divisor)).astype(np.float32)
         if spec.freq_scale is not None:
             if len(spec.freq_scale) != half:
                 raise ValueError("freq_scale must have rotary_dim/2 entries")

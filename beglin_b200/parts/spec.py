@@ -44,19 +44,28 @@ class PositionSpec:
     """Rotary position encoding: `rotary_dim` leading features of each head are rotated in pairs,
     (i, i + rotary_dim/2) for pairing "split_half" (qwen_infer.c:782-790) or (2i, 2i+1) for
     "interleaved" (qwen_infer.c:738-750); frequency i is theta^(-2i/rotary_dim) * freq_scale[i]
-    (qwen_infer.c:757-794).  kind "none" rotates nothing."""
+    (qwen_infer.c:757-794).  kind "none" rotates nothing.  `freq_divisor` d divides every frequency (positions
+    stretched d times, "linear scaling"); with it the frequencies are worked out in 64-bit and rounded once."""
     kind: str = "rope"
     rotary_dim: int = 0
     theta: float = 10000.0
     pairing: str = "split_half"
     freq_scale: Optional[Tuple[float, ...]] = None
+    freq_divisor: Optional[float] = None
 
 
 @dataclass(frozen=True)
 class AttentionSpec:
     """Grouped-query attention over a paged cache.  `window` None means all earlier positions; a
     number w means the last w positions, the token itself included.  `own_kv` False makes a mixer
-    that projects no keys and values of its own and reads the cache of another stage."""
+    that projects no keys and values of its own and reads the cache of another stage.
+
+    Options beyond the plain form, each off by default.  `v_head_dim`: values of another size than queries and
+    keys (a page then holds the keys of all kv heads followed by their values).  `qk_norm` "projection": the whole
+    query row and the whole key row of a token (all heads at once) are RMS-normed with weights of their own,
+    before the rotation, with `qk_norm_eps`.  `sink`: the softmax's denominator is enlarged by one, as if every
+    query saw one more key of score 0 that carries no value.  `gate` "elementwise": the joined heads are multiplied
+    by sigmoid of a further product of the mixer's input, feature by feature, before the output product."""
     hidden: int
     n_heads: int
     n_kv_heads: int
@@ -67,14 +76,43 @@ class AttentionSpec:
     window: Optional[int] = None
     scale: Optional[float] = None          # None: 1/sqrt(head_dim)  (qwen_infer.c:1488)
     own_kv: bool = True
+    v_head_dim: Optional[int] = None       # None: head_dim
+    qk_norm: Optional[str] = None          # None or "projection"
+    qk_norm_eps: float = 0.0
+    sink: bool = False
+    gate: Optional[str] = None             # None or "elementwise"
     kind: str = "gqa_attention"
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
 class SwiGLUSpec:
+    """down(act(gate(h)) * up(h)); `activation` "silu" or "gelu_tanh" (the tanh form of GELU)."""
     hidden: int
     intermediate: int
+    activation: str = "silu"
     kind: str = "swiglu"
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A sum over `top` of `experts` small feed-forwards, chosen per token by the largest router scores.  An expert
+    is down(act(up(h))) without a gate branch and without biases; `activation` "relu2" is the square of relu.
+    `router_activation` "sigmoid": the scores are sigmoid of the router's logits, which are computed in 32-bit.
+    `renormalize`: whether the chosen scores are divided by their sum.  `scale_input`: the score multiplies the
+    expert's input (True) or its output (False)."""
+    hidden: int
+    intermediate: int
+    experts: int
+    top: int
+    activation: str = "relu2"
+    router_activation: str = "sigmoid"
+    renormalize: bool = False
+    scale_input: bool = True
+    kind: str = "routed_experts"
 
 
 @dataclass(frozen=True)

@@ -22,13 +22,15 @@ class ResidualStream:
         self.ssq: Optional[torch.Tensor] = None        # float32 [parts, >= T]: partial sums of squares of x's rows
         self.history: Optional[torch.Tensor] = None    # float32 [slots, T, d]: the embedding output and the layer
         #                                                results so far, kept by a combiner that mixes over depth
+        self.lowp: Optional[torch.Tensor] = None       # x's rows in the compute type, as the kernel that last changed
+        #                                                x left them (for sublayers that read the stream un-normed)
 
     def owe(self, addend: torch.Tensor) -> None:
-        self.pending, self.ssq = addend, None
+        self.pending, self.ssq, self.lowp = addend, None, None
 
-    def updated(self, ssq: Optional[torch.Tensor]) -> None:
-        """x was changed in place by a fused product, which left these sums of squares."""
-        self.pending, self.ssq = None, ssq
+    def updated(self, ssq: Optional[torch.Tensor], lowp: Optional[torch.Tensor] = None) -> None:
+        """x was changed in place by a kernel, which left these sums of squares and this copy in the compute type."""
+        self.pending, self.ssq, self.lowp = None, ssq, lowp
 
 
 class NormedInput:
