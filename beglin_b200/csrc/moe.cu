@@ -1,8 +1,9 @@
 // Routed experts: what stands around the experts' products.
 //
 //   route_topk     per token, the `top` experts of largest score (score = sigmoid of the router's float logit, or the
-//                  logit itself), ties to the lower index; the weight of a choice is its score, divided by the sum of
-//                  the chosen scores when `renorm`.
+//                  logit itself), ties to the lower index; the logits are what is compared, since sigmoid keeps their
+//                  order but rounds large ones to equal scores.  The weight of a choice is its score, divided by the
+//                  sum of the chosen scores when `renorm`.
 //   route_sort     the step's assignments (token t, rank j) -> a = t * top + j are laid out expert by expert:
 //                  offsets[e] .. offsets[e + 1] are expert e's rows; row_of[a] is where assignment a went and
 //                  src_of[row] the assignment that row holds.  ONE CTA; the order inside an expert is whatever the
@@ -28,10 +29,8 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= T) return;
     float* sc = score_s + (size_t)warp * E;
-    for (int e = lane; e < E; e += 32) {
-        const float z = logits[(size_t)t * E + e];
-        sc[e] = sigmoid ? 1.0f / (1.0f + expf(-z)) : z;
-    }
+    // the choice is made on the logits: sigmoid keeps their order, but rounds large ones to the same score
+    for (int e = lane; e < E; e += 32) sc[e] = logits[(size_t)t * E + e];
     __syncwarp();
     float total = 0.0f;
     for (int j = 0; j < top; ++j) {
@@ -47,12 +46,13 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E
             const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
+        const float score = sigmoid ? 1.0f / (1.0f + expf(-best)) : best;
         if (lane == 0) {
             ids[(size_t)t * top + j] = arg;
-            weights[(size_t)t * top + j] = best;
+            weights[(size_t)t * top + j] = score;
             sc[arg] = -INFINITY;
         }
-        total += best;
+        total += score;
         __syncwarp();
     }
     if (renorm && lane < top) weights[(size_t)t * top + lane] /= total;

@@ -48,7 +48,9 @@ class AttentionMixerConfig:
         if self.window is not None:
             out["mask"] = {"size": self.window}
         if self.rot_dims:
-            out["rot"] = {"base": self.rot_base, "dims": self.rot_dims, "scaling": {"factor": self.rot_factor}}
+            out["rot"] = {"base": self.rot_base, "dims": self.rot_dims}
+            if self.rot_factor != 1.0:
+                out["rot"]["scaling"] = {"factor": self.rot_factor}
         return out
 
 

@@ -55,13 +55,13 @@ def turn_halves(v: torch.Tensor, positions: Sequence[int], base: float, dims: in
     the angle position * base^(-2i/dims) / divisor; the rest pass unchanged."""
     out = v.clone()
     half = dims // 2
-    for t, p in enumerate(positions):
-        for i in range(half):
-            a = p * (base ** (-2.0 * i / dims)) / divisor
-            c, s = math.cos(a), math.sin(a)
-            lo, hi = v[t, :, i], v[t, :, i + half]
-            out[t, :, i] = lo * c - hi * s
-            out[t, :, i + half] = hi * c + lo * s
+    pos = torch.tensor(list(positions), dtype=torch.float64)
+    for i in range(half):
+        a = pos * (base ** (-2.0 * i / dims)) / divisor
+        c, s = torch.cos(a)[:, None].to(v.dtype), torch.sin(a)[:, None].to(v.dtype)
+        lo, hi = v[:, :, i], v[:, :, i + half]
+        out[:, :, i] = lo * c - hi * s
+        out[:, :, i + half] = hi * c + lo * s
     return out
 
 
@@ -95,7 +95,7 @@ def attention(w: Dict[str, torch.Tensor], p: str, h: torch.Tensor, m: dict, eps:
         seen = list(range(first, t + 1))
         for head in range(H):
             g = head // per
-            scores = torch.stack([(q[t, head] * k[j, g]).sum() for j in seen]) * m["scale"]
+            scores = (k[seen, g] @ q[t, head]) * m["scale"]
             weights = sink_softmax(scores)
             joined[t, head * vdim:(head + 1) * vdim] = (weights[:, None] * v[seen, g]).sum(0)
     gate = torch.sigmoid(h @ w[p + "g"].T)
