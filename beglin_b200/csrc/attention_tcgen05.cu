@@ -72,7 +72,9 @@ __device__ __forceinline__ float at_ex2(float x) {
     return y;
 }
 
-template <int HD, int AT_BK>
+// SINK: the softmax's denominator is enlarged by one (a key of score 0 without a value): the final join takes 0 into the
+// maximum and exp2(0 - maximum) into the sum; nothing else differs, and the plain instance is compiled as before.
+template <int HD, int AT_BK, bool SINK = false>
 __global__ void __launch_bounds__(AT_THREADS)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParams p) {
     constexpr int AT_HALF = AT_BK / 2, AT_STAGES = 256 / AT_BK;
@@ -332,9 +334,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             tc_fence_after();
             const float2 other = ml_other[r];
             const float m_all = fmaxf(m, other.x);
-            const float m_ref = (m_all == -INFINITY) ? 0.0f : m_all;
+            const float m_ref = SINK ? fmaxf(m_all, 0.0f) : ((m_all == -INFINITY) ? 0.0f : m_all);
             const float a0 = at_ex2(m - m_ref), a1 = at_ex2(other.x - m_ref);
-            const float l_all = l * a0 + other.y * a1;
+            const float l_all = l * a0 + other.y * a1 + (SINK ? at_ex2(-m_ref) : 0.0f);
             const float inv = (real && l_all > 0.0f) ? 1.0f / l_all : 0.0f;
             const float w0 = a0 * inv, w1 = a1 * inv;
             const bool has1 = !ALT || n_tiles > 1;       // with one tile the second group's accumulator was never written
@@ -457,9 +459,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
     if (tid == 0 && failed && p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
 }
 
-template <int HD, int BK>
+template <int HD, int BK, bool SINK = false>
 static int at_launch(const CUtensorMap& map, const AttnTcParams& p, int n_qblk, cudaStream_t stream) {
-    auto kern = attention_tcgen05_kernel<HD, BK>;
+    auto kern = attention_tcgen05_kernel<HD, BK, SINK>;
     // Q, and two rings (keys, values) of 256 keys each
     const size_t smem = (size_t)(HD / 64) * AT_BM * 128 + (size_t)2 * 256 * (HD / 64) * 128 + 1024;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -488,10 +490,10 @@ extern "C" int bg_attention_tc_plan(int group, int hd, int page_size, int* bq_ou
     return BG_OK;
 }
 
-extern "C" int bg_attention_tc(const void* q, int q_stride, const void* kv_pool, int num_pages, int page_size,
-                               const int* block_table, int max_pages, const int* positions, const int* qblk, int n_qblk,
-                               void* out, int out_stride, int nh, int nkv, int hd, int window, float scale, int max_position,
-                               unsigned* status, cudaStream_t stream) {
+static int attention_tc(const void* q, int q_stride, const void* kv_pool, int num_pages, int page_size,
+                        const int* block_table, int max_pages, const int* positions, const int* qblk, int n_qblk,
+                        void* out, int out_stride, int nh, int nkv, int hd, int window, float scale, int max_position,
+                        bool sink, unsigned* status, cudaStream_t stream) {
     if (n_qblk <= 0) return BG_OK;
     if (nh % nkv != 0 || (hd != 64 && hd != 128) || nh / nkv > 128 || !(scale > 0.0f)) return BG_ERR_UNSUPPORTED;
     if (page_size < 1 || page_size > 64 || 64 % page_size != 0) return BG_ERR_UNSUPPORTED;
@@ -509,6 +511,27 @@ extern "C" int bg_attention_tc(const void* q, int q_stride, const void* kv_pool,
     if (rc != BG_OK) return rc;
     // tiles of 128 keys where a block may walk many of them (max_position bounds the positions of the step's rows)
     const bool wide = (window > 0 ? (window < max_position + 1 ? window : max_position + 1) : max_position + 1) >= at_wide_from();
+    if (sink) {
+        if (hd == 128) return wide ? at_launch<128, 128, true>(map, p, n_qblk, stream) : at_launch<128, 64, true>(map, p, n_qblk, stream);
+        return wide ? at_launch<64, 128, true>(map, p, n_qblk, stream) : at_launch<64, 64, true>(map, p, n_qblk, stream);
+    }
     if (hd == 128) return wide ? at_launch<128, 128>(map, p, n_qblk, stream) : at_launch<128, 64>(map, p, n_qblk, stream);
     return wide ? at_launch<64, 128>(map, p, n_qblk, stream) : at_launch<64, 64>(map, p, n_qblk, stream);
+}
+
+extern "C" int bg_attention_tc(const void* q, int q_stride, const void* kv_pool, int num_pages, int page_size,
+                               const int* block_table, int max_pages, const int* positions, const int* qblk, int n_qblk,
+                               void* out, int out_stride, int nh, int nkv, int hd, int window, float scale, int max_position,
+                               unsigned* status, cudaStream_t stream) {
+    return attention_tc(q, q_stride, kv_pool, num_pages, page_size, block_table, max_pages, positions, qblk, n_qblk, out, out_stride,
+                        nh, nkv, hd, window, scale, max_position, false, status, stream);
+}
+
+// The same with the softmax's denominator enlarged by one.
+extern "C" int bg_attention_tc_sink(const void* q, int q_stride, const void* kv_pool, int num_pages, int page_size,
+                                    const int* block_table, int max_pages, const int* positions, const int* qblk, int n_qblk,
+                                    void* out, int out_stride, int nh, int nkv, int hd, int window, float scale, int max_position,
+                                    unsigned* status, cudaStream_t stream) {
+    return attention_tc(q, q_stride, kv_pool, num_pages, page_size, block_table, max_pages, positions, qblk, n_qblk, out, out_stride,
+                        nh, nkv, hd, window, scale, max_position, true, status, stream);
 }

@@ -42,7 +42,7 @@ _SIGNATURES = {
     "bg_cast_rows": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
     "bg_qk_norm_rope_append": [_c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
                                _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int,
-                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "bg_route_logits": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_route_topk": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
     "bg_route_sort": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
@@ -52,7 +52,8 @@ _SIGNATURES = {
                         _c_int, _c_int, _c_int, _c_void_p],
     "bg_gemm_grouped_tc": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
                            _c_void_p, _c_int, _c_void_p, _c_void_p],
-    "bg_sigmoid_gate": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_sigmoid_gate": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_ll,
+                        _c_int, _c_int, _c_int, _c_void_p],
     "bg_attention_mma_plan": [_c_int, _c_int, _c_int, ctypes.POINTER(_c_int)],
     "bg_attention_mma_partial": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                                  _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -60,6 +61,8 @@ _SIGNATURES = {
     "bg_attention_tc_plan": [_c_int, _c_int, _c_int, ctypes.POINTER(_c_int)],
     "bg_attention_tc": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
                         _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p],
+    "bg_attention_tc_sink": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
+                             _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p],
     "bg_gemm_f32_nt": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_void_p],
     "bg_gemm_bf16_tn": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
@@ -448,7 +451,7 @@ def attention_wide_from(keys: int = 0) -> int:
 
 
 TC_ROWS_FOR = ("auto", "tcgen05")
-SINK_KERNELS = ("generic",)          # kernels whose softmax can take the enlarged denominator (`sink`)
+SINK_KERNELS = ("generic", "tc_rows", "mma_keys", "mma_rows")   # every kernel can take the enlarged denominator (`sink`)
 
 
 def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, decode_only: bool = False,
@@ -562,11 +565,12 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
     if kernel == "tc_rows":
         if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
             raise KernelError("attention: the tcgen05 kernel takes bfloat16 queries, caches and outputs")
-        _check(L.bg_attention_tc(_p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table),
-                                 block_table.shape[1], _p(positions), _p(qblk), n_qblk, _p(out), out.stride(0), nh, nkv,
-                                 hd, window, float(scale), int(max_position), _p(status), _stream()), "attention_tcgen05")
+        _check((L.bg_attention_tc_sink if sink else L.bg_attention_tc)(
+            _p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table), block_table.shape[1], _p(positions), _p(qblk),
+            n_qblk, _p(out), out.stride(0), nh, nkv, hd, window, float(scale), int(max_position), _p(status), _stream()),
+            "attention_tcgen05")
         return
-    if kernel == "mma_rows":
+    if kernel == "mma_rows" and not sink:
         if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
             raise KernelError("attention: the tensor-core kernel takes bfloat16 queries, caches and outputs")
         _check(L.bg_attention_mma_partial(_p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table),
@@ -576,7 +580,7 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
         return
     if kernel == "mma_keys":
         split, n_splits = 0, decode_splits(n_qblk * nkv, max_position + 1)
-        if n_splits == 1:                        # one CTA walks all keys of its (request, kv head) and writes the rows
+        if n_splits == 1 and not sink:           # one CTA walks all keys of its (request, kv head) and writes the rows
             if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
                 raise KernelError("attention: the tensor-core kernel takes bfloat16 queries, caches and outputs")
             _check(L.bg_attention_mma_partial(_p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table),
@@ -593,13 +597,16 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
                                       _p(block_table), block_table.shape[1], _p(positions), _p(qblk), n_qblk,
                                       _p(part_o), _p(part_ml), n_splits, n_splits, nh, nkv, hd, vd, window, split, tile,
                                       bq, float(scale), _p(status), _stream()), "attention_partial")
-    elif kernel == "mma_keys":
+    elif kernel in ("mma_keys", "mma_rows"):
+        # (the kernels that write finished rows know the plain softmax only: with the enlarged denominator their rows
+        # go through partial results, also when there is one range of keys, and the merge adds the sink's share)
         if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16:
             raise KernelError("attention: the tensor-core kernel takes bfloat16 queries and caches")
         _check(L.bg_attention_mma_partial(_p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table),
                                           block_table.shape[1], _p(positions), _p(qblk) if qblk is not None else None,
                                           n_qblk, _p(part_o),
-                                          _p(part_ml), n_splits, n_splits, nh, nkv, hd, window, split, 1,
+                                          _p(part_ml), n_splits, n_splits, nh, nkv, hd, window, split,
+                                          1 if kernel == "mma_keys" else 0,
                                           float(scale), None, 0, _p(status), _stream()), "attention_mma_partial")
     else:
         raise KernelError(f"unknown attention kernel '{kernel}'")
@@ -1206,25 +1213,27 @@ def qk_norm_rope_append(src: torch.Tensor, q_out: torch.Tensor, n_rows: int, nh:
                         interleaved: bool, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                         cos_sin: Optional[torch.Tensor], positions: torch.Tensor, row_req: torch.Tensor,
                         block_table: torch.Tensor, kv_pool: Optional[torch.Tensor], page_size: int,
-                        status: Optional[torch.Tensor]) -> None:
+                        status: Optional[torch.Tensor], stored: Optional[int] = None) -> None:
     """Rows [q | k | v | ...] of `src` ([T, W], or float partial sums [parts, T, W]): RMS norm of the whole q row and of
     the whole k row with the float weights given (None: no norm), rotation of the first `rot` features of every head,
-    q into q_out [T, nh*hd], k and v into the paged cache (a page: keys [nkv, page, hd], then values [nkv, page, vd])."""
+    q into q_out [T, nh*hd], k and v into the paged cache (a page: keys [nkv, page, hd], then values [nkv, page, vd]).
+    With `stored` = D every head of q, k and v is stored D features wide, zeros behind its own."""
+    qs, ks, vs = (hd, hd, vd) if stored is None else (stored, stored, stored)
     _cuda(src, q_out, q_weight, k_weight, cos_sin, positions, row_req, block_table, kv_pool)
     _i32(positions, "positions"); _i32(row_req, "row_req"); _i32(block_table, "block_table")
     parts, stride = _parts(src, "qk_norm_rope_append: src")
     need = nh * hd + (nkv * (hd + vd) if kv_pool is not None else 0)
     if src.stride(-1) != 1 or src.shape[-1] < need or src.shape[-2] < n_rows:
         raise KernelError(f"qk_norm_rope_append: rows of {src.shape[-1]} features cannot hold q, k, v ({need})")
-    if q_out.stride(1) != 1 or q_out.shape[1] < nh * hd or q_out.shape[0] < n_rows:
+    if q_out.stride(1) != 1 or q_out.shape[1] < nh * qs or q_out.shape[0] < n_rows:
         raise KernelError("qk_norm_rope_append: q_out must be [T, nh*hd]")
     for w, n in ((q_weight, nh * hd), (k_weight, nkv * hd)):
         if w is not None and (w.dtype != torch.float32 or w.numel() != n or not w.is_contiguous()):
             raise KernelError("qk_norm_rope_append: norm weights are contiguous float32 of the projection's width")
     num_pages = 0
     if kv_pool is not None:
-        if not kv_pool.is_contiguous() or kv_pool[0].numel() != nkv * page_size * (hd + vd):
-            raise KernelError(f"qk_norm_rope_append: a page of {tuple(kv_pool.shape)} does not hold {nkv} x {page_size} x ({hd} + {vd})")
+        if not kv_pool.is_contiguous() or kv_pool[0].numel() != nkv * page_size * (ks + vs):
+            raise KernelError(f"qk_norm_rope_append: a page of {tuple(kv_pool.shape)} does not hold {nkv} x {page_size} x ({ks} + {vs})")
         num_pages = kv_pool.shape[0]
     if rot > 0 and (cos_sin is None or cos_sin.shape[0] < n_rows or cos_sin.shape[1] != rot // 2 or cos_sin.dtype != torch.float32):
         raise KernelError("qk_norm_rope_append: cos_sin must be float32 [T, rot/2, 2]")
@@ -1233,20 +1242,26 @@ def qk_norm_rope_append(src: torch.Tensor, q_out: torch.Tensor, n_rows: int, nh:
                                             _p(q_weight), _p(k_weight), float(eps), _p(cos_sin), _p(positions), _p(row_req),
                                             _p(block_table), block_table.shape[1], _p(kv_pool),
                                             _dt(kv_pool) if kv_pool is not None else _dt(q_out), num_pages, page_size, n_rows, nh,
-                                            nkv, hd, vd, rot, 1 if interleaved else 0, _p(status), _stream()),
+                                            nkv, hd, vd, rot, 1 if interleaved else 0, qs, ks, vs, _p(status), _stream()),
                "qk_norm_rope_append")
 
 
-def sigmoid_gate(out: torch.Tensor, gate: torch.Tensor, col0: int, n: int) -> None:
-    """out[t, j] *= sigmoid(gate[t, col0 + j]) for j < n; gate is [T, W] or its float partial sums [parts, T, W]."""
-    _cuda(out, gate)
+def sigmoid_gate(out: torch.Tensor, gate: torch.Tensor, col0: int, n: int, src: Optional[torch.Tensor] = None,
+                 vd: Optional[int] = None, head_stride: Optional[int] = None) -> None:
+    """out[t, j] = src[t, (j // vd) * head_stride + j % vd] * sigmoid(gate[t, col0 + j]) for j < n; gate is [T, W] or its float
+    partial sums [parts, T, W].  Without `src`, out itself is gated in place."""
+    _cuda(out, gate, src)
     parts, stride = _parts(gate, "sigmoid_gate: gate")
     T = out.shape[0]
+    if src is None:
+        src, vd, head_stride = out, n, n
     if out.dim() != 2 or out.stride(1) != 1 or out.shape[1] < n or gate.stride(-1) != 1 or gate.shape[-2] < T or col0 + n > gate.shape[-1]:
         raise KernelError("sigmoid_gate: out [T, >= n], gate rows that hold n values from col0")
+    if src.dtype != out.dtype or src.stride(1) != 1 or src.shape[0] < T or n % vd or src.shape[1] < (n // vd - 1) * head_stride + vd:
+        raise KernelError("sigmoid_gate: src of out's type with n / vd heads, head_stride features apart")
     with phase("activation"):
-        _check(lib().bg_sigmoid_gate(_p(out), _dt(out), out.stride(0), _p(gate), _dt(gate), gate.stride(-2), parts, stride, col0, T, n,
-                                     _stream()), "sigmoid_gate")
+        _check(lib().bg_sigmoid_gate(_p(out), _dt(out), out.stride(0), _p(src), src.stride(0), vd, head_stride, _p(gate), _dt(gate),
+                                     gate.stride(-2), parts, stride, col0, T, n, _stream()), "sigmoid_gate")
 
 
 # ---------------------------------------------------------------------------------------------------- routed experts

@@ -5,7 +5,10 @@
 //   (2i, 2i + 1) when interleaved); the rest pass unchanged
 //   q goes to q_out [T, nh*hd]; k and v go to the token's place in the paged cache.
 // A page holds the keys of all kv heads, [nkv][page_size][hd], followed by their values, [nkv][page_size][vd]; with
-// vd == hd that is the layout [2][nkv][page_size][hd] of the other attention kernels.
+// vd == hd that is the layout [2][nkv][page_size][hd] of the other attention kernels.  The heads may be stored wider than
+// they are (`qs`, `ks`, `vs` features apart for queries, keys and values, the rest zeros): a head of 96 or of 128 + 32
+// features then fills the 64 or 128 that the tensor-core attention kernels take, and a zero adds nothing to a score or
+// to a weighted sum.
 // The source rows are [q | k | v | ...] as the product left them (any trailing columns are ignored), or the float
 // partial sums of a split-K product, added in index order.  Statistics, scaling and rotation are float; a value is
 // rounded once, when it is stored.  One block per token, its q and k held in shared memory.
@@ -21,6 +24,7 @@ struct QkNormRopeParams {
     const int* positions; const int* row_req; const int* block_table; int max_pages;
     void* pool; int num_pages, page_size;                    // null pool: the rows hold queries only
     int nh, nkv, hd, vd, rot, interleaved;
+    int qs, ks, vs;                                          // stored width of a query, key and value head (>= hd, hd, vd)
     unsigned* status;
 };
 
@@ -42,10 +46,10 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(QkNormRopePara
         if (page < 0 || page >= p.num_pages) {
             if (p.status && threadIdx.x == 0) atomicOr(p.status, BG_STATUS_BAD_PAGE);
         } else {
-            const size_t page_elems = (size_t)p.nkv * p.page_size * (p.hd + p.vd);
+            const size_t page_elems = (size_t)p.nkv * p.page_size * (p.ks + p.vs);
             const int slot = pos % p.page_size;
-            k_base = (long long)((size_t)page * page_elems + (size_t)slot * p.hd);
-            v_base = (long long)((size_t)page * page_elems + (size_t)p.nkv * p.page_size * p.hd + (size_t)slot * p.vd);
+            k_base = (long long)((size_t)page * page_elems + (size_t)slot * p.ks);
+            v_base = (long long)((size_t)page * page_elems + (size_t)p.nkv * p.page_size * p.ks + (size_t)slot * p.vs);
         }
     }
     pdl_wait();
@@ -80,20 +84,31 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(QkNormRopePara
             const float c = cs[2 * pair], s = cs[2 * pair + 1], o = qk_s[partner];
             v = low ? v * c - o * s : v * c + o * s;
         }
-        if (i < qd) qo[j] = from_float<TQ>(v);
-        else if (k_base >= 0) pool[k_base + (size_t)h * p.page_size * p.hd + f] = from_float<TC>(v);
+        if (i < qd) qo[(size_t)h * p.qs + f] = from_float<TQ>(v);
+        else if (k_base >= 0) pool[k_base + (size_t)h * p.page_size * p.ks + f] = from_float<TC>(v);
     }
     if (v_base >= 0) {
         for (int i = threadIdx.x; i < vdd; i += blockDim.x) {
             const int h = i / p.vd, f = i - h * p.vd;
-            pool[v_base + (size_t)h * p.page_size * p.vd + f] = from_float<TC>(sum_parts(row + qd + kd + i, p.parts, p.part_stride));
+            pool[v_base + (size_t)h * p.page_size * p.vs + f] = from_float<TC>(sum_parts(row + qd + kd + i, p.parts, p.part_stride));
         }
     }
+    // heads stored wider than they are: zeros behind every head
+    const int qpad = p.qs - p.hd, kpad = p.ks - p.hd, vpad = p.vs - p.vd;
+    for (int i = threadIdx.x; i < p.nh * qpad; i += blockDim.x) qo[(size_t)(i / qpad) * p.qs + p.hd + i % qpad] = from_float<TQ>(0.0f);
+    if (k_base >= 0)
+        for (int i = threadIdx.x; i < p.nkv * kpad; i += blockDim.x)
+            pool[k_base + (size_t)(i / kpad) * p.page_size * p.ks + p.hd + i % kpad] = from_float<TC>(0.0f);
+    if (v_base >= 0)
+        for (int i = threadIdx.x; i < p.nkv * vpad; i += blockDim.x)
+            pool[v_base + (size_t)(i / vpad) * p.page_size * p.vs + p.vd + i % vpad] = from_float<TC>(0.0f);
 }
 
-// out[t][j] *= sigmoid(gate[t][col0 + j]) for j < n: the gate is a column range of a wider row (or of its partial sums).
+// out[t][j] = src[t][(j / vd) * head_stride + j % vd] * sigmoid(gate[t][col0 + j]) for j < n: the gate is a column range of
+// a wider row (or of its partial sums); the source's heads may be stored wider than they are (out == src when they are not).
 template <typename TG, typename TO>
-__global__ void sigmoid_gate_kernel(TO* __restrict__ out, int out_stride, const TG* __restrict__ gate, int gate_stride, int parts,
+__global__ void sigmoid_gate_kernel(TO* __restrict__ out, int out_stride, const TO* __restrict__ src, int src_stride, int vd,
+                                    int head_stride, const TG* __restrict__ gate, int gate_stride, int parts,
                                     size_t part_stride, int col0, int rows, int n) {
     pdl_launch();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -103,8 +118,8 @@ __global__ void sigmoid_gate_kernel(TO* __restrict__ out, int out_stride, const 
     pdl_wait();
     if (idle) return;
     const float g = sum_parts(gate + t * gate_stride + col0 + j, parts, part_stride);
-    TO* o = out + t * out_stride + j;
-    *o = from_float<TO>(to_float(*o) / (1.0f + expf(-g)));
+    const float v = to_float(src[t * src_stride + (size_t)(j / vd) * head_stride + j % vd]);
+    out[t * out_stride + j] = from_float<TO>(v / (1.0f + expf(-g)));
 }
 
 }  // namespace bg
@@ -129,15 +144,17 @@ extern "C" int bg_qk_norm_rope_append(const void* src, int src_dtype, int src_st
                                       void* q_out, int q_dtype, int q_stride, const float* wq, const float* wk, float eps,
                                       const float* cos_sin, const int* positions, const int* row_req, const int* block_table,
                                       int max_pages, void* pool, int cache_dtype, int num_pages, int page_size, int T, int nh,
-                                      int nkv, int hd, int vd, int rot, int interleaved, unsigned* status, cudaStream_t stream) {
+                                      int nkv, int hd, int vd, int rot, int interleaved, int qs, int ks, int vs, unsigned* status,
+                                      cudaStream_t stream) {
     if (T <= 0) return BG_OK;
     if (rot < 0 || rot > hd || rot % 2 || parts < 1 || (rot > 0 && !cos_sin) || ((wq == nullptr) != (wk == nullptr))) return BG_ERR_SHAPE;
+    if (qs < hd || ks < hd || vs < vd) return BG_ERR_SHAPE;
     if (src_dtype != q_dtype && src_dtype != BG_DTYPE_F32) return BG_ERR_DTYPE;
     QkNormRopeParams p;
     p.src = src; p.src_stride = src_stride; p.parts = parts; p.part_stride = (size_t)part_stride; p.q_out = q_out;
     p.q_stride = q_stride; p.wq = wq; p.wk = wk; p.eps = eps; p.cos_sin = cos_sin; p.positions = positions; p.row_req = row_req;
     p.block_table = block_table; p.max_pages = max_pages; p.pool = pool; p.num_pages = num_pages; p.page_size = page_size;
-    p.nh = nh; p.nkv = nkv; p.hd = hd; p.vd = vd; p.rot = rot; p.interleaved = interleaved; p.status = status;
+    p.nh = nh; p.nkv = nkv; p.hd = hd; p.vd = vd; p.rot = rot; p.interleaved = interleaved; p.qs = qs; p.ks = ks; p.vs = vs; p.status = status;
     if (!pool) cache_dtype = q_dtype;
     if (cache_dtype != q_dtype) return BG_ERR_DTYPE;            // queries and cache are both of the compute type
     if (q_dtype == BG_DTYPE_F32) {
@@ -148,15 +165,16 @@ extern "C" int bg_qk_norm_rope_append(const void* src, int src_dtype, int src_st
     return qk_norm_rope_launch<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(p, T, stream);
 }
 
-extern "C" int bg_sigmoid_gate(void* out, int out_dtype, int out_stride, const void* gate, int gate_dtype, int gate_stride,
-                               int parts, long long part_stride, int col0, int rows, int n, cudaStream_t stream) {
+extern "C" int bg_sigmoid_gate(void* out, int out_dtype, int out_stride, const void* src, int src_stride, int vd, int head_stride,
+                               const void* gate, int gate_dtype, int gate_stride, int parts, long long part_stride, int col0,
+                               int rows, int n, cudaStream_t stream) {
     if (rows <= 0 || n <= 0) return BG_OK;
-    if (parts < 1) return BG_ERR_SHAPE;
+    if (parts < 1 || vd <= 0 || head_stride < vd) return BG_ERR_SHAPE;
     const size_t total = (size_t)rows * n;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     BG_DISPATCH_DTYPE(gate_dtype, TG, BG_DISPATCH_DTYPE(out_dtype, TO,
-        launch(sigmoid_gate_kernel<TG, TO>, dim3(blocks), dim3(256), 0, stream, (TO*)out, out_stride, (const TG*)gate, gate_stride,
-               parts, (size_t)part_stride, col0, rows, n)));
+        launch(sigmoid_gate_kernel<TG, TO>, dim3(blocks), dim3(256), 0, stream, (TO*)out, out_stride, (const TO*)src, src_stride, vd,
+               head_stride, (const TG*)gate, gate_stride, parts, (size_t)part_stride, col0, rows, n)));
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

@@ -52,7 +52,9 @@ class DecoderModel:
             if stage.cache is None:
                 for _, family, cls, pspec in registry.layer_slots(self.spec.layers[stage.layer]):
                     if family == "mixer":
-                        need = cls.cache_need(pspec)
+                        # (a mixer whose pages depend on the compute type is asked with the context)
+                        need = cls.cache_need(pspec, self.ctx) if getattr(cls, "cache_need_takes_context", False) \
+                            else cls.cache_need(pspec)
             needs.append(need)
         return needs
 

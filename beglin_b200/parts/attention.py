@@ -56,10 +56,31 @@ class GQAAttention:
             roles.append(TensorRole("g_proj.weight", (od, spec.hidden), True, True))
         return roles
 
+    cache_need_takes_context = True        # cache_need(spec, ctx): what a page holds depends on the compute type
+
     @staticmethod
-    def cache_need(spec: AttentionSpec) -> Optional[PagedKVNeed]:
+    def stored_head(spec: AttentionSpec, ctx: Optional[BuildContext]) -> Optional[int]:
+        """The width at which the heads of an extended attention are stored so that the tensor-core kernels take them (64
+        or 128 features, zeros behind a head's own; a zero adds nothing to a score or to a weighted sum), or None where
+        they are stored as they are: in float32, for heads that fit already, and where the padding would more than
+        double the cache."""
+        if ctx is None or ctx.compute_dtype != torch.bfloat16 or ctx.attention == "generic":
+            return None
+        hd, vd = spec.head_dim, spec.value_dim
+        if spec.qk_norm is None and vd == hd and spec.gate is None:
+            return None                        # the plain form keeps its layout
+        if hd == vd and hd in (64, 128):
+            return None
+        stored = 64 if max(hd, vd) <= 64 else 128
+        return stored if max(hd, vd) <= 128 and stored <= hd + vd else None
+
+    @staticmethod
+    def cache_need(spec: AttentionSpec, ctx: Optional[BuildContext] = None) -> Optional[PagedKVNeed]:
         if not spec.own_kv:
             return None
+        stored = GQAAttention.stored_head(spec, ctx)
+        if stored is not None:
+            return PagedKVNeed(spec.n_kv_heads, stored, spec.window)
         return PagedKVNeed(spec.n_kv_heads, spec.head_dim, spec.window,
                            None if spec.value_dim == spec.head_dim else spec.value_dim)
 
@@ -96,9 +117,10 @@ class GQAAttention:
         scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(float(self.hd))
         self.scale = float(np.float32(scale))
         # (a softmax with the enlarged denominator runs the kernels that have it)
-        prefer = ctx.attention if not spec.sink or ctx.attention in ops.SINK_KERNELS else "generic"
-        self.plans = {d: ops.attention_plan(self.nh // self.nkv, self.hd, ctx.cache_dtype, d, prefer,
-                                            ctx.page_size, vd=self.vd) for d in (False, True)}
+        self.stored = self.stored_head(spec, ctx)
+        khd, kvd_ = (self.hd, self.vd) if self.stored is None else (self.stored, self.stored)     # what the kernels see
+        self.plans = {d: ops.attention_plan(self.nh // self.nkv, khd, ctx.cache_dtype, d, ctx.attention,
+                                            ctx.page_size, vd=kvd_) for d in (False, True)}
         self.window = int(spec.window) if spec.window else 0
         # the fused q/k/v product can rotate and append itself: whole heads rotated in halves, a cache of its own
         # in bfloat16
@@ -113,13 +135,14 @@ class GQAAttention:
         it) and None is returned; without, the addend is returned."""
         T = batch.n_rows
         qkv = None
+        khd, kvd_ = (self.hd, self.vd) if self.stored is None else (self.stored, self.stored)
         if self.extended:
             qkv = self.qkv.of(h)
-            q = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=qkv.device)
+            q = torch.empty((T, self.nh * khd), dtype=self.ctx.compute_dtype, device=qkv.device)
             ops.qk_norm_rope_append(qkv, q, T, self.nh, self.nkv, self.hd, self.vd, self.position.rotary_dim,
                                     self.position.interleaved, self.q_norm, self.k_norm, self.spec.qk_norm_eps,
                                     self.position.table(batch), batch.positions, batch.row_req, cache.block_table,
-                                    cache.pool, cache.page_size, self.ctx.status)
+                                    cache.pool, cache.page_size, self.ctx.status, stored=self.stored)
         elif self.rope_in_product and self.qkv.rope_fuses(T, self.hd):
             # a step of few tokens: rotation and cache append inside the q/k/v product
             q = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=self.ctx.device)
@@ -136,12 +159,17 @@ class GQAAttention:
         if qblk is None and kernel != "mma_keys":
             batch.implicit_blocks = False              # this kernel wants the list
             qblk, n_qblk = batch.query_blocks(bq)
-        out = torch.empty((T, self.od), dtype=self.ctx.compute_dtype, device=q.device)
+        out = torch.empty((T, self.nh * kvd_), dtype=self.ctx.compute_dtype, device=q.device)
         ops.attention(q, q.stride(0), cache.pool, cache.block_table, batch.positions, qblk, n_qblk,
-                      batch.max_position, T, self.nh, self.nkv, self.hd, self.window, self.ctx.kv_split, tile, bq,
-                      self.scale, out, self.ctx.status, kernel, vd=self.vd, sink=self.spec.sink)
-        if self.spec.gate is not None:
+                      batch.max_position, T, self.nh, self.nkv, khd, self.window, self.ctx.kv_split, tile, bq,
+                      self.scale, out, self.ctx.status, kernel, vd=kvd_, sink=self.spec.sink)
+        if self.spec.gate is not None and self.stored is None:
             ops.sigmoid_gate(out, qkv, self.gate_col, self.od)
+        elif self.spec.gate is not None:               # the gate's kernel also drops the zeros behind every head
+            wide, out = out, torch.empty((T, self.od), dtype=self.ctx.compute_dtype, device=q.device)
+            ops.sigmoid_gate(out, qkv, self.gate_col, self.od, src=wide, vd=self.vd, head_stride=self.stored)
+        elif self.stored is not None:
+            out = out.view(T, self.nh, self.stored)[:, :, :self.vd].reshape(T, self.od)
         if stream is None:
             return self.o_proj.partial(out)
         self.o_proj.into(out, stream)

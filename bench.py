@@ -369,7 +369,25 @@ def qwen2_like(width, heads, layers, vocab=32768):
             "use_sliding_window": False, "hidden_act": "silu", "max_position_embeddings": 32768}
 
 
+# The Nadilorn decoder beside the Qwen2 decoder at equal layer sizes (--design nadilorn): grouped-query attention with
+# keys of 128 features and values of 128 or 64, a norm over the whole query and key rows, rotation of half of every head,
+# a window of 1,024 positions, the enlarged softmax denominator and the output gate; the first layer with a gated GELU
+# feed-forward, the others with eight routed experts of which two are chosen (inner size such that the two chosen have
+# the weights of the Qwen2 layer's feed-forward).  Random weights.
+def nadilorn_config(width, heads, layers, vocab=32768, vdim=128):
+    kv = max(1, heads // 4 if heads % 4 == 0 and heads > 12 else heads // 6)
+    mixer = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": vdim, "scale": 128 ** -0.5, "mask": {"size": 1024},
+             "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0}}}
+    im = (8 * width // 3) // 128 * 128
+    dense = {"kind": "dense", "ff": im}
+    moe = {"kind": "moe", "expert": {"ff": (3 * im // 4) // 64 * 64}, "router": {"experts": 8, "top": 2}}
+    return {"architecture": "Nadilorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": dense if i == 0 else moe} for i in range(layers)]}
+
+
 DESIGN_SIZES = {"1536": (1536, 12, 8), "4096": (4096, 32, 4)}      # width -> (width, heads, layers)
+DESIGNS = {"sukisun": lambda w, h, l: sukisun_config(w, h, l), "nadilorn": lambda w, h, l: nadilorn_config(w, h, l),
+           "nadilorn-v64": lambda w, h, l: nadilorn_config(w, h, l, vdim=64)}
 
 
 def phase_times(eng, fn):
@@ -405,7 +423,10 @@ def design_point(cfg, pk, batch, context, steps, warmup, tokens):
     out["decode_tok_s"] = round(batch * 1000.0 / ms, 1)
     out["decode_ms"] = round(ms, 4)
     out["decode_launches_per_step"] = launches // max(1, steps)
-    step_bytes = eng.model.weight_bytes() + batch * (context - steps / 2.0) * out["cache_bytes_per_token"]
+    # (a layer with a window reads no more of a request's positions than the window holds)
+    windows = [l["mixer"].get("mask", {}).get("size") for l in cfg.get("layers", []) if isinstance(l.get("mixer"), dict)]
+    seen = min([context - steps / 2.0] + [w for w in windows if w]) if windows and all(windows) else context - steps / 2.0
+    step_bytes = eng.model.weight_bytes() + batch * seen * out["cache_bytes_per_token"]
     out["decode_frac_of_hbm"] = round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
     rids = [("cls", i) for i in range(batch)]
     fill_cache(eng, rids, context - 8, seed=4)
@@ -419,7 +440,7 @@ def design_timeline(args):
     """The kernels of one decoding step (or of one prompt step of 2,048 tokens) of the design at the first of the sizes."""
     from beglin_b200 import Engine
     width, heads, layers = DESIGN_SIZES[args.design_sizes.split(",")[0]]
-    eng = Engine.random(sukisun_config(width, heads, layers), seed=0, dtype="bfloat16", device="cuda:0",
+    eng = Engine.random(DESIGNS[args.design](width, heads, layers), seed=0, dtype="bfloat16", device="cuda:0",
                         max_tokens=args.batch * (args.context + 64), page_size=64, max_requests=args.batch,
                         max_context=args.context + 64)
     if args.timeline == "prefill":
@@ -439,9 +460,9 @@ def design_comparison(args, pk):
     rows = {}
     for name in args.design_sizes.split(","):
         width, heads, layers = DESIGN_SIZES[name]
-        for label, cfg in (("sukisun", sukisun_config(width, heads, layers)), ("qwen2", qwen2_like(width, heads, layers))):
+        for label, cfg in ((args.design, DESIGNS[args.design](width, heads, layers)), ("qwen2", qwen2_like(width, heads, layers))):
             rows[f"{label}_{name}"] = design_point(cfg, pk, args.batch, args.context, min(args.steps, 32), args.warmup, 2048)
-    print(json.dumps({"design": "sukisun beside qwen2 at equal layer sizes", "dtype": "bf16", "batch": args.batch,
+    print(json.dumps({"design": f"{args.design} beside qwen2 at equal layer sizes", "dtype": "bf16", "batch": args.batch,
                       "context": args.context, "data": "synthetic (seeded uniform token ids, random weights)",
                       "peaks": pk, "clocks": clocks.stop(), "points": rows}))
     return 0
@@ -464,7 +485,7 @@ def main():
     ap.add_argument("--timeline", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                     help="instead of the measurement: print the kernels of one decode step (or of one prompt step of "
                          "2,048 tokens) with their device times")
-    ap.add_argument("--design", default=None, choices=["sukisun"],
+    ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="instead of the headline measurement: this design beside Qwen2 at equal layer sizes, prefill and "
                          "decode, with the device time per kernel class")
     ap.add_argument("--design-sizes", default="1536,4096", help="widths to compare at, of " + ",".join(sorted(DESIGN_SIZES)))

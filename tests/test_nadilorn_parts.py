@@ -149,7 +149,7 @@ def plain_attention_rows(q, keys, vals, positions, scale, window, sink=True):
     return out
 
 
-def run_attention(q, keys, vals, lengths, new, scale, window, sink, dtype, page=16, split=64):
+def run_attention(q, keys, vals, lengths, new, scale, window, sink, dtype, page=16, split=64, prefer="generic", decode=False):
     """Requests with `lengths[r]` cached positions of which the last `new[r]` are the step's rows."""
     o = ops()
     H, hd = q[0].shape[1:]
@@ -168,7 +168,7 @@ def run_attention(q, keys, vals, lengths, new, scale, window, sink, dtype, page=
     rows = torch.cat([q[r] for r in range(len(lengths))]).to(dtype)
     T = rows.shape[0]
     positions = torch.cat([torch.arange(n - m, n) for n, m in zip(lengths, new)]).int()
-    kernel, bq, tile = o.attention_plan(H // G, hd, dtype, False, "generic", page, vd=vd)
+    kernel, bq, tile = o.attention_plan(H // G, hd, dtype, decode, prefer, page, vd=vd)
     blocks = []
     r0 = 0
     for r, m in enumerate(new):
@@ -178,8 +178,29 @@ def run_attention(q, keys, vals, lengths, new, scale, window, sink, dtype, page=
     qblk = torch.tensor(blocks, dtype=torch.int32, device=DEV)
     out = torch.empty(T, H * vd, dtype=dtype, device=DEV)
     o.attention(rows.reshape(T, H * hd).to(DEV), H * hd, pool.to(DEV), table.to(DEV), positions.to(DEV), qblk, len(blocks),
-                int(positions.max()), T, H, G, hd, window or 0, split, tile, bq, scale, out, None, kernel, vd=vd, sink=sink)
+                int(positions.max()), T, H, G, hd, window or 0, split, tile, bq, scale, out, o.new_status(DEV), kernel, vd=vd, sink=sink)
     return out.reshape(T, H, vd)
+
+
+@pytest.mark.parametrize("H,G,hd,window", [(6, 2, 64, 100), (4, 1, 128, None), (2, 2, 128, 70), (8, 2, 64, 300)])
+@pytest.mark.parametrize("how", ["tcgen05", "mma", "mma_decode"])
+@pytest.mark.parametrize("sink", [True, False])
+def test_tensor_core_attention_with_sink(H, G, hd, window, how, sink):
+    """The tensor-core kernels (tcgen05 for portions, mma.sync for portions and for single tokens) with the enlarged
+    denominator and a window, pages of 16 and of 64, against the plain softmax."""
+    g = torch.Generator().manual_seed(H * hd)
+    decode = how == "mma_decode"
+    lengths, new = ([150, 333, 9, 600], [1, 1, 1, 1]) if decode else ([150, 333, 9], [37, 130, 9])
+    rnd = lambda *s: torch.randn(*s, generator=g, dtype=torch.float64).to(torch.bfloat16).double()
+    keys, vals = [rnd(n, G, hd) for n in lengths], [rnd(n, G, hd) for n in lengths]
+    q = [rnd(m, H, hd) for m in new]
+    scale = 1.3 / math.sqrt(hd)
+    for page in (16, 64):
+        got = run_attention(q, keys, vals, lengths, new, scale, window, sink, torch.bfloat16, page=page, split=256,
+                            prefer="mma" if decode else how, decode=decode)
+        want = torch.cat([plain_attention_rows(q[r], keys[r], vals[r], range(n - m, n), scale, window, sink=sink)
+                          for r, (n, m) in enumerate(zip(lengths, new))])
+        close(got, want, 1e-2)
 
 
 @pytest.mark.parametrize("H,G,hd,vd,window", [(3, 1, 10, 6, 13), (4, 2, 12, 12, 40), (2, 2, 16, 24, None), (6, 3, 64, 32, 100),
