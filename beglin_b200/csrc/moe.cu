@@ -20,18 +20,10 @@
 
 namespace bg {
 
-__global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E, int top, int sigmoid, int renorm,
-                                  int* __restrict__ ids, float* __restrict__ weights) {
-    extern __shared__ float score_s[];                     // [warps][E]
-    pdl_launch();
-    pdl_wait();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= T) return;
-    float* sc = score_s + (size_t)warp * E;
-    // the choice is made on the logits: sigmoid keeps their order, but rounds large ones to the same score
-    for (int e = lane; e < E; e += 32) sc[e] = logits[(size_t)t * E + e];
-    __syncwarp();
+// One warp chooses for one token: `sc` holds the token's E logits in shared memory and is used up.  The choice is made on the
+// logits: sigmoid keeps their order, but rounds large ones to the same score.
+__device__ __forceinline__ void choose_experts(float* sc, int E, int top, int sigmoid, int renorm, int* __restrict__ ids,
+                                               float* __restrict__ weights, size_t t, int lane) {
     float total = 0.0f;
     for (int j = 0; j < top; ++j) {
         float best = -INFINITY;
@@ -56,6 +48,59 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E
         __syncwarp();
     }
     if (renorm && lane < top) weights[(size_t)t * top + lane] /= total;
+}
+
+__global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E, int top, int sigmoid, int renorm,
+                                  int* __restrict__ ids, float* __restrict__ weights) {
+    extern __shared__ float score_s[];                     // [warps][E]
+    pdl_launch();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    float* sc = score_s + (size_t)warp * E;
+    for (int e = lane; e < E; e += 32) sc[e] = logits[(size_t)t * E + e];
+    __syncwarp();
+    choose_experts(sc, E, top, sigmoid, renorm, ids, weights, (size_t)t, lane);
+}
+
+// The router of a step in one kernel: a block takes ROUTE_TOKENS tokens; each of its warps takes experts in turn and
+// forms the float logits of all the block's tokens against that expert's row (the row is read once per block; a lane
+// walks the features 32 apart and the warp adds up, so a logit's order of summation depends on nothing but the width);
+// then warp w chooses for token w.  `logits_out`, when given, also receives the logits.
+constexpr int ROUTE_TOKENS = 8;
+template <typename TI>
+__global__ void __launch_bounds__(32 * ROUTE_TOKENS)
+route_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W, int T, int d, int E, int top, int sigmoid, int renorm,
+             int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ logits_out) {
+    extern __shared__ float logit_s[];                     // [ROUTE_TOKENS][E]
+    pdl_launch();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * ROUTE_TOKENS;
+    const int n = min(ROUTE_TOKENS, T - t0);
+    for (int e = warp; e < E; e += ROUTE_TOKENS) {
+        float acc[ROUTE_TOKENS];
+#pragma unroll
+        for (int j = 0; j < ROUTE_TOKENS; ++j) acc[j] = 0.0f;
+        const float* w = W + (size_t)e * d;
+        for (int k = lane; k < d; k += 32) {
+            const float wk = w[k];
+#pragma unroll
+            for (int j = 0; j < ROUTE_TOKENS; ++j)
+                if (j < n) acc[j] = fmaf(to_float(h[(size_t)(t0 + j) * ldh + k]), wk, acc[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < ROUTE_TOKENS; ++j) {
+            const float v = warp_sum(acc[j]);
+            if (lane == 0 && j < n) {
+                logit_s[j * E + e] = v;
+                if (logits_out) logits_out[(size_t)(t0 + j) * E + e] = v;
+            }
+        }
+    }
+    __syncthreads();
+    if (warp < n) choose_experts(logit_s + warp * E, E, top, sigmoid, renorm, ids, weights, (size_t)(t0 + warp), lane);
 }
 
 __global__ void __launch_bounds__(1024)
@@ -269,6 +314,20 @@ extern "C" int bg_route_topk(const float* logits, int T, int E, int top, int sig
     if (smem > 40 * 1024) return BG_ERR_UNSUPPORTED;
     launch(route_topk_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), smem, stream, logits, T, E, top, sigmoid, renorm, ids,
            weights);
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+// The router in one kernel: float logits of h [T, d] (either type, row stride ldh) against W [E, d] float, and the choice.
+extern "C" int bg_route(const void* h, int h_dtype, int ldh, const float* W, int T, int d, int E, int top, int sigmoid, int renorm,
+                        int* ids, float* weights, float* logits_out, cudaStream_t stream) {
+    if (T <= 0) return BG_OK;
+    if (E <= 0 || top <= 0 || top > E || top > 32 || d <= 0) return BG_ERR_SHAPE;
+    const size_t smem = (size_t)ROUTE_TOKENS * E * sizeof(float);
+    if (smem > 40 * 1024) return BG_ERR_UNSUPPORTED;
+    const dim3 grid((T + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(32 * ROUTE_TOKENS);
+    BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_kernel<TI>, grid, block, smem, stream, (const TI*)h, ldh, W, T, d, E, top, sigmoid,
+                                          renorm, ids, weights, logits_out));
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

@@ -45,6 +45,8 @@ _SIGNATURES = {
                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "bg_route_logits": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_route_topk": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "bg_route": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+                 _c_void_p, _c_void_p],
     "bg_route_sort": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "bg_route_gather": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_route_combine": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
@@ -1293,6 +1295,25 @@ def route_topk(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch
     with phase("router"):
         _check(lib().bg_route_topk(_p(logits), T, E, top, 1 if sigmoid else 0, 1 if renorm else 0, _p(ids), _p(weights), _stream()),
                "route_topk")
+
+
+def route(h: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor, sigmoid: bool = True,
+          renorm: bool = False, logits: Optional[torch.Tensor] = None) -> None:
+    """`route_logits` and `route_topk` as one kernel: h [T, d] in either type, router float32 [E, d], ids int32 [T, top],
+    weights float32 [T, top]; `logits`, when given, receives the float logits [T, E]."""
+    _cuda(h, router, ids, weights, logits)
+    T, d = h.shape
+    E = router.shape[0]
+    _i32(ids, "ids")
+    if router.dtype != torch.float32 or router.shape[1] != d or h.stride(1) != 1 or not router.is_contiguous() \
+            or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top) or weights.dtype != torch.float32 \
+            or not ids.is_contiguous() or not weights.is_contiguous():
+        raise KernelError("route: h [T, d], router float32 [E, d], ids int32 [T, top], weights float32 [T, top]")
+    if logits is not None and (logits.dtype != torch.float32 or tuple(logits.shape) != (T, E) or not logits.is_contiguous()):
+        raise KernelError("route: logits float32 [T, E]")
+    with phase("router"):
+        _check(lib().bg_route(_p(h), _dt(h), h.stride(0), _p(router), T, d, E, top, 1 if sigmoid else 0, 1 if renorm else 0, _p(ids),
+                              _p(weights), _p(logits), _stream()), "route")
 
 
 def route_sort(ids: torch.Tensor, E: int, offsets: torch.Tensor, row_of: torch.Tensor, src_of: torch.Tensor) -> None:

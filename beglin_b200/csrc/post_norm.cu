@@ -5,6 +5,8 @@
 // the stream as it is, un-normed: writing it here saves a kernel of its own.
 // One block per row; the row of y is held in shared memory between the two passes.  Every row's sum of squares is
 // added up in an order fixed by the width alone, so a row does not depend on what else the step holds.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace bg {
@@ -72,6 +74,54 @@ rmsnorm_add_vec4_kernel(float* __restrict__ x, const float* __restrict__ y, int 
     }
 }
 
+// Many rows of a bfloat16 step: a warp per row, the row's values in registers (ITER chunks of eight a lane), one trip to
+// memory.  The float32 path keeps ONE kernel for every number of rows, so that a row's statistics are added up in the same
+// order whatever else the step holds.
+template <typename TY, typename TW, int ITER>
+__global__ void __launch_bounds__(256)
+rmsnorm_add_warp_kernel(float* __restrict__ x, const TY* __restrict__ y, int parts, size_t part_stride, const TW* __restrict__ w,
+                        float eps, __nv_bfloat16* __restrict__ lowp, int n_rows, int d) {
+    pdl_launch();
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const bool idle = warp >= n_rows;
+    const size_t base = (size_t)(idle ? 0 : warp) * d;
+    const int d8 = d >> 3;
+    pdl_wait();
+    if (idle) return;
+    float v[ITER][8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int c = lane + 32 * i;
+        if (c < d8) {
+            load8(y + base + 8 * c, v[i]);
+            for (int pp = 1; pp < parts; ++pp) {
+                float u[8];
+                load8(y + (size_t)pp * part_stride + base + 8 * c, u);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[i][e] += u[e];
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+        }
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int c = lane + 32 * i;
+        if (c < d8) {
+            float xv[8], wv[8];
+            load8(x + base + 8 * c, xv);
+            load8(w + 8 * c, wv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) xv[e] += v[i][e] * inv * wv[e];
+            store8(x + base + 8 * c, xv);
+            if (lowp) store8(lowp + base + 8 * c, xv);
+        }
+    }
+}
+
 template <typename TO>
 __global__ void cast_rows_kernel(const float* __restrict__ x, TO* __restrict__ out, long long n) {
     pdl_launch();
@@ -91,7 +141,21 @@ static int rmsnorm_add_launch(float* x, const void* y, int parts, size_t part_st
     if (smem > 200 * 1024) return BG_ERR_SHAPE;
     const bool vec = std::is_same<TY, float>::value && d % 4 == 0 && part_stride % 4 == 0 && (uintptr_t)x % 16 == 0 &&
                      (uintptr_t)y % 16 == 0 && (uintptr_t)lowp % 8 == 0;
-    if (vec) {
+    const bool rows_in_registers = std::is_same<TL, __nv_bfloat16>::value && lowp && n_rows >= 64 && d % 8 == 0 && d <= 8 * 32 * 16 &&
+                                   part_stride % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)w % 16 == 0 &&
+                                   (uintptr_t)lowp % 16 == 0;
+    if (rows_in_registers) {
+        const int iter = (d / 8 + 31) / 32;
+        const unsigned blocks = (unsigned)((n_rows + 7) / 8);
+#define BG_NORM_ADD_WARP(IT)                                                                                                \
+        launch(rmsnorm_add_warp_kernel<TY, TW, IT>, dim3(blocks), dim3(256), 0, stream, x, (const TY*)y, parts, part_stride,     \
+               (const TW*)w, eps, (__nv_bfloat16*)lowp, n_rows, d)
+        if (iter <= 2) BG_NORM_ADD_WARP(2);
+        else if (iter <= 4) BG_NORM_ADD_WARP(4);
+        else if (iter <= 8) BG_NORM_ADD_WARP(8);
+        else BG_NORM_ADD_WARP(16);
+#undef BG_NORM_ADD_WARP
+    } else if (vec) {
         auto kern = rmsnorm_add_vec4_kernel<TW, TL>;
         if (smem > BG_SMEM_OPT_IN) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         int threads = ((d / 4 + 31) / 32) * 32;

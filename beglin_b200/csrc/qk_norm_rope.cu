@@ -12,6 +12,8 @@
 // The source rows are [q | k | v | ...] as the product left them (any trailing columns are ignored), or the float
 // partial sums of a split-K product, added in index order.  Statistics, scaling and rotation are float; a value is
 // rounded once, when it is stored.  One block per token, its q and k held in shared memory.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace bg {
@@ -104,6 +106,107 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(QkNormRopePara
             pool[v_base + (size_t)(i / vpad) * p.page_size * p.vs + p.vd + i % vpad] = from_float<TC>(0.0f);
 }
 
+// The same for sizes in multiples of 8 (heads, stored widths, the rotated part's halves, the source's columns) with the
+// rotation in halves: every access moves eight values, 16 bytes of bfloat16.  A thread's eight features lie in one head
+// and on one side of the rotated part, so their partners are eight consecutive features too.
+template <typename TS, typename TQ, typename TC>
+__global__ void __launch_bounds__(256) qk_norm_rope_append_vec8_kernel(QkNormRopeParams p) {
+    extern __shared__ float qk_s[];
+    __shared__ float red[32];
+    pdl_launch();
+    const int t = blockIdx.x;
+    const int qd = p.nh * p.hd, kd = p.pool ? p.nkv * p.hd : 0, vdd = p.pool ? p.nkv * p.vd : 0;
+    const int half = p.rot / 2;
+    const TS* row = (const TS*)p.src + (size_t)t * p.src_stride;
+    const int pos = p.positions[t];
+    long long k_base = -1, v_base = -1;
+    if (p.pool) {
+        const int req = p.row_req[t];
+        const int page = p.block_table[(size_t)req * p.max_pages + pos / p.page_size];
+        if (page < 0 || page >= p.num_pages) {
+            if (p.status && threadIdx.x == 0) atomicOr(p.status, BG_STATUS_BAD_PAGE);
+        } else {
+            const size_t page_elems = (size_t)p.nkv * p.page_size * (p.ks + p.vs);
+            const int slot = pos % p.page_size;
+            k_base = (long long)((size_t)page * page_elems + (size_t)slot * p.ks);
+            v_base = (long long)((size_t)page * page_elems + (size_t)p.nkv * p.page_size * p.ks + (size_t)slot * p.vs);
+        }
+    }
+    pdl_wait();
+    float ssq = 0.0f, ssk = 0.0f;
+    for (int i = threadIdx.x * 8; i < qd + kd; i += blockDim.x * 8) {
+        float v[8];
+        load8(row + i, v);
+        for (int pp = 1; pp < p.parts; ++pp) {
+            float u[8];
+            load8(row + (size_t)pp * p.part_stride + i, u);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] += u[e];
+        }
+        float ss = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { qk_s[i + e] = v[e]; ss += v[e] * v[e]; }
+        if (i < qd) ssq += ss; else ssk += ss;
+    }
+    float inv_q = 1.0f, inv_k = 1.0f;
+    if (p.wq) {
+        ssq = block_sum(ssq, red);
+        ssk = block_sum(ssk, red);
+        inv_q = 1.0f / sqrtf(ssq / (float)qd + p.eps);
+        inv_k = kd > 0 ? 1.0f / sqrtf(ssk / (float)kd + p.eps) : 0.0f;
+    }
+    __syncthreads();
+    const float* cs = p.cos_sin ? p.cos_sin + (size_t)t * half * 2 : nullptr;
+    TQ* qo = (TQ*)p.q_out + (size_t)t * p.q_stride;
+    TC* pool = (TC*)p.pool;
+    for (int i = threadIdx.x * 8; i < qd + kd; i += blockDim.x * 8) {
+        const bool is_q = i < qd;
+        const int j = is_q ? i : i - qd;
+        const int h = j / p.hd, f = j - h * p.hd;
+        const float inv = is_q ? inv_q : inv_k;
+        const float* w = p.wq ? (is_q ? p.wq + j : p.wk + j) : nullptr;
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = w ? qk_s[i + e] * inv * w[e] : qk_s[i + e];
+        if (f < p.rot) {
+            const bool low = f < half;
+            const int pair = low ? f : f - half, partner = low ? i + half : i - half;
+            const float* wp = w ? (low ? w + half : w - half) : nullptr;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float o = wp ? qk_s[partner + e] * inv * wp[e] : qk_s[partner + e];
+                const float c = cs[2 * (pair + e)], sn = cs[2 * (pair + e) + 1];
+                v[e] = low ? v[e] * c - o * sn : v[e] * c + o * sn;
+            }
+        }
+        if (is_q) store8(qo + (size_t)h * p.qs + f, v);
+        else if (k_base >= 0) store8(pool + k_base + (size_t)h * p.page_size * p.ks + f, v);
+    }
+    if (v_base >= 0) {
+        for (int i = threadIdx.x * 8; i < vdd; i += blockDim.x * 8) {
+            const int h = i / p.vd, f = i - h * p.vd;
+            float v[8];
+            load8(row + qd + kd + i, v);
+            for (int pp = 1; pp < p.parts; ++pp) {
+                float u[8];
+                load8(row + (size_t)pp * p.part_stride + qd + kd + i, u);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += u[e];
+            }
+            store8(pool + v_base + (size_t)h * p.page_size * p.vs + f, v);
+        }
+    }
+    const float zero[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    const int qpad = (p.qs - p.hd) / 8, kpad = (p.ks - p.hd) / 8, vpad = (p.vs - p.vd) / 8;
+    for (int i = threadIdx.x; i < p.nh * qpad; i += blockDim.x) store8(qo + (size_t)(i / qpad) * p.qs + p.hd + 8 * (i % qpad), zero);
+    if (k_base >= 0)
+        for (int i = threadIdx.x; i < p.nkv * kpad; i += blockDim.x)
+            store8(pool + k_base + (size_t)(i / kpad) * p.page_size * p.ks + p.hd + 8 * (i % kpad), zero);
+    if (v_base >= 0)
+        for (int i = threadIdx.x; i < p.nkv * vpad; i += blockDim.x)
+            store8(pool + v_base + (size_t)(i / vpad) * p.page_size * p.vs + p.vd + 8 * (i % vpad), zero);
+}
+
 // out[t][j] = src[t][(j / vd) * head_stride + j % vd] * sigmoid(gate[t][col0 + j]) for j < n: the gate is a column range of
 // a wider row (or of its partial sums); the source's heads may be stored wider than they are (out == src when they are not).
 template <typename TG, typename TO>
@@ -122,13 +225,45 @@ __global__ void sigmoid_gate_kernel(TO* __restrict__ out, int out_stride, const 
     out[t * out_stride + j] = from_float<TO>(v / (1.0f + expf(-g)));
 }
 
+// Eight values a thread (n, vd, the strides and col0 in multiples of 8, everything 16-byte aligned).
+template <typename TG, typename TO>
+__global__ void sigmoid_gate_vec8_kernel(TO* __restrict__ out, int out_stride, const TO* __restrict__ src, int src_stride, int vd,
+                                         int head_stride, const TG* __restrict__ gate, int gate_stride, int parts,
+                                         size_t part_stride, int col0, int rows, int n) {
+    pdl_launch();
+    const int n8 = n >> 3;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool idle = idx >= (size_t)rows * n8;
+    const size_t t = idle ? 0 : idx / n8;
+    const int j = idle ? 0 : 8 * (int)(idx - t * n8);
+    pdl_wait();
+    if (idle) return;
+    float g[8], v[8];
+    load8(gate + t * gate_stride + col0 + j, g);
+    for (int pp = 1; pp < parts; ++pp) {
+        float u[8];
+        load8(gate + (size_t)pp * part_stride + t * gate_stride + col0 + j, u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) g[e] += u[e];
+    }
+    load8(src + t * src_stride + (size_t)(j / vd) * head_stride + j % vd, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = __fdividef(v[e], 1.0f + __expf(-g[e]));
+    store8(out + t * out_stride + j, v);
+}
+
 }  // namespace bg
 
 using namespace bg;
 
 template <typename TS, typename TQ, typename TC>
 static int qk_norm_rope_launch(const QkNormRopeParams& p, int T, cudaStream_t stream) {
-    auto kern = qk_norm_rope_append_kernel<TS, TQ, TC>;
+    const int width = p.nh * p.hd + (p.pool ? p.nkv * (p.hd + p.vd) : 0);
+    const bool vec = !std::is_same<TQ, float>::value && !p.interleaved && p.hd % 8 == 0 && p.vd % 8 == 0 && p.rot % 16 == 0 &&
+                     p.qs % 8 == 0 && p.ks % 8 == 0 && p.vs % 8 == 0 && p.src_stride % 8 == 0 && p.part_stride % 8 == 0 &&
+                     p.q_stride % 8 == 0 && (uintptr_t)p.src % 16 == 0 && (uintptr_t)p.q_out % 16 == 0 && (uintptr_t)p.pool % 16 == 0 &&
+                     (!p.wq || ((uintptr_t)p.wq % 16 == 0 && (uintptr_t)p.wk % 16 == 0)) && width > 0;
+    auto kern = vec ? qk_norm_rope_append_vec8_kernel<TS, TQ, TC> : qk_norm_rope_append_kernel<TS, TQ, TC>;
     const size_t smem = (size_t)(p.nh * p.hd + (p.pool ? p.nkv * p.hd : 0)) * sizeof(float);
     if (smem > 200 * 1024) return BG_ERR_SHAPE;
     if (smem > BG_SMEM_OPT_IN) {
@@ -172,6 +307,18 @@ extern "C" int bg_sigmoid_gate(void* out, int out_dtype, int out_stride, const v
     if (parts < 1 || vd <= 0 || head_stride < vd) return BG_ERR_SHAPE;
     const size_t total = (size_t)rows * n;
     const unsigned blocks = (unsigned)((total + 255) / 256);
+    const bool vec = out_dtype == BG_DTYPE_BF16 && n % 8 == 0 && vd % 8 == 0 && head_stride % 8 == 0 && out_stride % 8 == 0 &&
+                     src_stride % 8 == 0 && gate_stride % 8 == 0 && col0 % 8 == 0 && part_stride % 8 == 0 &&
+                     (uintptr_t)out % 16 == 0 && (uintptr_t)src % 16 == 0 && (uintptr_t)gate % 16 == 0;
+    if (vec) {
+        const unsigned vblocks = (unsigned)((total / 8 + 255) / 256);
+        BG_DISPATCH_DTYPE(gate_dtype, TG,
+            launch(sigmoid_gate_vec8_kernel<TG, __nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream, (__nv_bfloat16*)out, out_stride,
+                   (const __nv_bfloat16*)src, src_stride, vd, head_stride, (const TG*)gate, gate_stride, parts, (size_t)part_stride,
+                   col0, rows, n));
+        BG_LAUNCH_CHECK();
+        return BG_OK;
+    }
     BG_DISPATCH_DTYPE(gate_dtype, TG, BG_DISPATCH_DTYPE(out_dtype, TO,
         launch(sigmoid_gate_kernel<TG, TO>, dim3(blocks), dim3(256), 0, stream, (TO*)out, out_stride, (const TO*)src, src_stride, vd,
                head_stride, (const TG*)gate, gate_stride, parts, (size_t)part_stride, col0, rows, n)));

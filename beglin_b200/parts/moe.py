@@ -47,12 +47,10 @@ class RoutedExperts:
             h = h.tensor()
         s, dev, ct = self.spec, h.device, self.ctx.compute_dtype
         T, A = h.shape[0], h.shape[0] * s.top
-        logits = torch.empty((T, s.experts), dtype=torch.float32, device=dev)
-        ops.route_logits(h, self.router, logits)
         ints = torch.empty((3 * A + s.experts + 1,), dtype=torch.int32, device=dev)
         ids, row_of, src_of, offsets = ints[:A].view(T, s.top), ints[A:2 * A], ints[2 * A:3 * A], ints[3 * A:]
         weights = torch.empty((T, s.top), dtype=torch.float32, device=dev)
-        ops.route_topk(logits, s.top, ids, weights, sigmoid=s.router_activation == "sigmoid", renorm=s.renormalize)
+        ops.route(h, self.router, s.top, ids, weights, sigmoid=s.router_activation == "sigmoid", renorm=s.renormalize)
         ops.route_sort(ids.view(-1), s.experts, offsets, row_of, src_of)
         xp = torch.empty((A, s.hidden), dtype=ct, device=dev)
         ops.route_gather(h, weights.view(-1), src_of, xp, s.top, scale=s.scale_input)

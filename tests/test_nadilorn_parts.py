@@ -304,6 +304,14 @@ def test_router_logits_and_choice():
     o.route_topk(z.to(DEV), top, ids, w, sigmoid=True, renorm=True)
     s = torch.sigmoid(want.values[:, :top])
     close(w, s / s.sum(1, keepdim=True), 2e-6)
+    # logits and choice as one kernel, rows in either type, a number of tokens that is no multiple of a block's
+    for rows in (h, hb):
+        o.route(rows.to(DEV), router.to(DEV), top, ids, w, logits=logits)
+        zz = rows.double() @ router.double().T
+        close(logits, zz, 2e-6)
+        srt = torch.sort(logits.cpu().double(), dim=1, descending=True, stable=True)
+        assert torch.equal(ids.cpu().long(), srt.indices[:, :top])
+        close(w, torch.sigmoid(srt.values[:, :top]), 2e-6)
 
 
 @pytest.mark.parametrize("A,E", [(1, 1), (7, 3), (300, 5), (5000, 64), (64, 200)])
