@@ -68,7 +68,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E
 // forms the float logits of all the block's tokens against that expert's row (the row is read once per block; a lane
 // walks the features 32 apart and the warp adds up, so a logit's order of summation depends on nothing but the width);
 // then warp w chooses for token w.  `logits_out`, when given, also receives the logits.
-constexpr int ROUTE_TOKENS = 8;
+constexpr int ROUTE_TOKENS = 8, ROUTE_UNROLL = 8;
 template <typename TI>
 __global__ void __launch_bounds__(32 * ROUTE_TOKENS)
 route_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W, int T, int d, int E, int top, int sigmoid, int renorm,
@@ -84,11 +84,22 @@ route_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W, int
 #pragma unroll
         for (int j = 0; j < ROUTE_TOKENS; ++j) acc[j] = 0.0f;
         const float* w = W + (size_t)e * d;
-        for (int k = lane; k < d; k += 32) {
-            const float wk = w[k];
+        // ROUTE_UNROLL features a lane at a time: all their loads go out before the first product (one feature at a time
+        // cost a trip to memory per feature: 58 us for 1,536 features, whatever the number of tokens)
+        for (int k0 = lane; k0 < d; k0 += 32 * ROUTE_UNROLL) {
+            float wk[ROUTE_UNROLL], hv[ROUTE_UNROLL][ROUTE_TOKENS];
 #pragma unroll
-            for (int j = 0; j < ROUTE_TOKENS; ++j)
-                if (j < n) acc[j] = fmaf(to_float(h[(size_t)(t0 + j) * ldh + k]), wk, acc[j]);
+            for (int u = 0; u < ROUTE_UNROLL; ++u) {
+                const int k = k0 + 32 * u;
+                wk[u] = k < d ? w[k] : 0.0f;
+#pragma unroll
+                for (int j = 0; j < ROUTE_TOKENS; ++j)
+                    hv[u][j] = (k < d && j < n) ? to_float(h[(size_t)(t0 + j) * ldh + k]) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < ROUTE_UNROLL; ++u)
+#pragma unroll
+                for (int j = 0; j < ROUTE_TOKENS; ++j) acc[j] = fmaf(hv[u][j], wk[u], acc[j]);
         }
 #pragma unroll
         for (int j = 0; j < ROUTE_TOKENS; ++j) {
@@ -101,6 +112,52 @@ route_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W, int
     }
     __syncthreads();
     if (warp < n) choose_experts(logit_s + warp * E, E, top, sigmoid, renorm, ids, weights, (size_t)(t0 + warp), lane);
+}
+
+// The same for a width that is a multiple of 8 and 16-byte aligned rows: warp w of a block takes token w, four experts at a
+// time; a lane walks the token's features in chunks of eight, 32 chunks apart (16-byte loads: one of the token's row, which
+// stays in the first-level cache from expert to expert, and two of each expert's row), and the warp adds up.  The walk
+// through the features one at a time above cost 53 us for 1,536 features whatever the number of tokens.
+template <typename TI>
+__global__ void __launch_bounds__(32 * ROUTE_TOKENS)
+route_vec8_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W, int T, int d, int E, int top, int sigmoid,
+                  int renorm, int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ logits_out) {
+    extern __shared__ float logit_s[];                     // [ROUTE_TOKENS][E]
+    pdl_launch();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * ROUTE_TOKENS + warp;
+    if (t >= T) return;                                    // (after the wait; the block's warps meet at no barrier)
+    const TI* row = h + (size_t)t * ldh;
+    float* sc = logit_s + warp * E;
+    const int d8 = d >> 3;
+    for (int e0 = 0; e0 < E; e0 += 4) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 2
+        for (int c = lane; c < d8; c += 32) {
+            float hv[8];
+            load8(row + 8 * c, hv);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (e0 + u < E) {
+                    float wv[8];
+                    load8(W + (size_t)(e0 + u) * d + 8 * c, wv);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[u] = fmaf(hv[i], wv[i], acc[u]);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float v = warp_sum(acc[u]);
+            if (lane == 0 && e0 + u < E) {
+                sc[e0 + u] = v;
+                if (logits_out) logits_out[(size_t)t * E + e0 + u] = v;
+            }
+        }
+    }
+    __syncwarp();
+    choose_experts(sc, E, top, sigmoid, renorm, ids, weights, (size_t)t, lane);
 }
 
 __global__ void __launch_bounds__(1024)
@@ -326,8 +383,12 @@ extern "C" int bg_route(const void* h, int h_dtype, int ldh, const float* W, int
     const size_t smem = (size_t)ROUTE_TOKENS * E * sizeof(float);
     if (smem > 40 * 1024) return BG_ERR_UNSUPPORTED;
     const dim3 grid((T + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(32 * ROUTE_TOKENS);
-    BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_kernel<TI>, grid, block, smem, stream, (const TI*)h, ldh, W, T, d, E, top, sigmoid,
-                                          renorm, ids, weights, logits_out));
+    if (d % 8 == 0 && ldh % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)W % 16 == 0)
+        BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_vec8_kernel<TI>, grid, block, smem, stream, (const TI*)h, ldh, W, T, d, E, top,
+                                              sigmoid, renorm, ids, weights, logits_out));
+    else
+        BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_kernel<TI>, grid, block, smem, stream, (const TI*)h, ldh, W, T, d, E, top, sigmoid,
+                                              renorm, ids, weights, logits_out));
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

@@ -39,6 +39,8 @@ _SIGNATURES = {
                            _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_rmsnorm_add": [_c_void_p, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_int,
                        _c_int, _c_void_p],
+    "bg_rmsnorm_add_routed": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_float, _c_void_p,
+                              _c_int, _c_int, _c_int, _c_void_p],
     "bg_cast_rows": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
     "bg_qk_norm_rope_append": [_c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
                                _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int,
@@ -1200,6 +1202,26 @@ def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: flo
     with phase("rmsnorm"):
         _check(lib().bg_rmsnorm_add(_p(x), _p(y), _dt(y), parts, stride, _p(weight), _dt(weight), float(eps), _p(lowp),
                                     _dt(lowp) if lowp is not None else F32, T, d, _stream()), "rmsnorm_add")
+
+
+def rmsnorm_add_routed(x: torch.Tensor, yp: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor, top: int, scale: bool,
+                       weight: torch.Tensor, eps: float, lowp: Optional[torch.Tensor] = None) -> None:
+    """`route_combine` and `rmsnorm_add` as one kernel: x += rmsnorm(y) * weight with y[t] the sum over j < top of
+    (weights[t * top + j] *) yp[row_of[t * top + j]], ranks in index order; yp float32 [T * top, d]."""
+    _cuda(x, yp, row_of, weights, weight, lowp)
+    _i32(row_of, "row_of")
+    T, d = x.shape
+    if x.dtype != torch.float32 or yp.dtype != torch.float32 or weights.dtype != torch.float32 or not x.is_contiguous() \
+            or not yp.is_contiguous() or tuple(yp.shape) != (T * top, d) or row_of.numel() != T * top or weights.numel() != T * top:
+        raise KernelError("rmsnorm_add_routed: x float32 [T, d], yp float32 [T * top, d], row_of and weights [T * top]")
+    if weight.numel() != d or not weight.is_contiguous():
+        raise KernelError(f"rmsnorm_add_routed: weight has {weight.numel()} of {d} values")
+    if lowp is not None and (tuple(lowp.shape) != (T, d) or not lowp.is_contiguous()):
+        raise KernelError("rmsnorm_add_routed: lowp must be contiguous and shaped like x")
+    with phase("rmsnorm"):
+        _check(lib().bg_rmsnorm_add_routed(_p(x), _p(yp), _p(row_of), _p(weights), top, 1 if scale else 0, _p(weight), _dt(weight),
+                                           float(eps), _p(lowp), _dt(lowp) if lowp is not None else F32, T, d, _stream()),
+               "rmsnorm_add_routed")
 
 
 def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:

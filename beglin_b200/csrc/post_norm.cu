@@ -122,6 +122,54 @@ rmsnorm_add_warp_kernel(float* __restrict__ x, const TY* __restrict__ y, int par
     }
 }
 
+// The same behind routed experts: a token's y is the sum of the rows that its `top` chosen experts produced,
+// y[t] = sum_j (weights[a] *) yp[row_of[a]], a = t * top + j, added in rank order; the sum that a kernel of its own would
+// write and this one read back is formed here.  `vec`: the width is a multiple of 4 and everything 16-byte aligned.
+template <typename TW, typename TL>
+__global__ void __launch_bounds__(256)
+rmsnorm_add_routed_kernel(float* __restrict__ x, const float* __restrict__ yp, const int* __restrict__ row_of,
+                          const float* __restrict__ weights, int top, int scale, const TW* __restrict__ w, float eps,
+                          TL* __restrict__ lowp, int d, int vec) {
+    extern __shared__ float row_buf[];
+    __shared__ float red[32];
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const size_t base = (size_t)t * d;
+    float ss = 0.0f;
+    if (vec) {
+        for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int j = 0; j < top; ++j) {
+                const int a = t * top + j;
+                const float4 v = *reinterpret_cast<const float4*>(yp + (size_t)row_of[a] * d + i);
+                const float f = scale ? weights[a] : 1.0f;
+                acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
+            }
+            *reinterpret_cast<float4*>(row_buf + i) = acc;
+            ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            float acc = 0.0f;
+            for (int j = 0; j < top; ++j) {
+                const int a = t * top + j;
+                const float v = yp[(size_t)row_of[a] * d + i];
+                acc += scale ? weights[a] * v : v;
+            }
+            row_buf[i] = acc;
+            ss += acc * acc;
+        }
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = x[base + i] + row_buf[i] * inv * to_float(w[i]);
+        x[base + i] = v;
+        if (lowp) lowp[base + i] = from_float<TL>(v);
+    }
+}
+
 template <typename TO>
 __global__ void cast_rows_kernel(const float* __restrict__ x, TO* __restrict__ out, long long n) {
     pdl_launch();
@@ -179,6 +227,30 @@ extern "C" int bg_rmsnorm_add(float* x, const void* y, int y_dtype, int parts, l
     if (!lowp) lowp_dtype = BG_DTYPE_F32;
     BG_DISPATCH_DTYPE(y_dtype, TY, BG_DISPATCH_DTYPE(w_dtype, TW, BG_DISPATCH_DTYPE(lowp_dtype, TL,
         return (rmsnorm_add_launch<TY, TW, TL>(x, y, parts, (size_t)part_stride, w, eps, lowp, n_rows, d, stream)))));
+    return BG_OK;
+}
+
+// x [T][d] += norm(sum over a token's `top` rows of yp [T * top][d] float) * w; lowp may be null.
+extern "C" int bg_rmsnorm_add_routed(float* x, const float* yp, const int* row_of, const float* weights, int top, int scale,
+                                     const void* w, int w_dtype, float eps, void* lowp, int lowp_dtype, int n_rows, int d,
+                                     cudaStream_t stream) {
+    if (n_rows <= 0) return BG_OK;
+    if (top < 1 || d <= 0) return BG_ERR_SHAPE;
+    const size_t smem = (size_t)d * sizeof(float);
+    if (smem > 200 * 1024) return BG_ERR_SHAPE;
+    if (!lowp) lowp_dtype = BG_DTYPE_F32;
+    const int vec = d % 4 == 0 && (uintptr_t)yp % 16 == 0;
+    int threads = ((d / 4 + 31) / 32) * 32;
+    threads = threads > 256 ? 256 : (threads < 32 ? 32 : threads);
+#define BG_ROUTED(TW, TL)                                                                                                   \
+    do {                                                                                                                    \
+        auto kern = rmsnorm_add_routed_kernel<TW, TL>;                                                                      \
+        if (smem > BG_SMEM_OPT_IN) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+        launch(kern, dim3(n_rows), dim3(threads), smem, stream, x, yp, row_of, weights, top, scale, (const TW*)w, eps, (TL*)lowp, d, vec); \
+    } while (0)
+    BG_DISPATCH_DTYPE(w_dtype, TW, BG_DISPATCH_DTYPE(lowp_dtype, TL, BG_ROUTED(TW, TL)));
+#undef BG_ROUTED
+    BG_LAUNCH_CHECK();
     return BG_OK;
 }
 

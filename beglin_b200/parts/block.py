@@ -98,7 +98,10 @@ class PostNormBlock:
         a = self.mixer.forward(self.rows(stream, dtype), batch, cache)
         stream.updated(None, self.mixer_norm.norm_add(stream.x, a, want_lowp=True))
         if self.feed_forward is not None:
-            m = self.feed_forward.forward(self.rows(stream, dtype), batch)
+            if getattr(self.feed_forward, "gives_rows", False) and hasattr(self.feed_forward_norm, "norm_add"):
+                m = self.feed_forward.forward(self.rows(stream, dtype), batch, summed=False)    # the norm adds the experts' rows up
+            else:
+                m = self.feed_forward.forward(self.rows(stream, dtype), batch)
             stream.updated(None, self.feed_forward_norm.norm_add(stream.x, m, want_lowp=True))
 
 

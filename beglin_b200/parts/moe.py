@@ -8,6 +8,7 @@ row alone (each output summed over the inner size in index order), so it does no
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Dict, List
 
 import torch
@@ -16,6 +17,18 @@ from ..csrc import ops
 from .context import BuildContext
 from .registry import register_feed_forward
 from .spec import RoutedExpertsSpec, TensorRole
+
+
+@dataclass
+class RoutedRows:
+    """The experts' results before they are added up per token: rows [T * top, hidden] float32 laid out expert by expert,
+    `row_of[t * top + j]` the row of token t's rank j, `weights` the chosen scores, `scale` whether they still multiply.
+    A norm that stands behind the experts adds the rows up itself (`RMSNorm.norm_add`)."""
+    rows: torch.Tensor
+    row_of: torch.Tensor
+    weights: torch.Tensor
+    top: int
+    scale: bool
 
 
 @register_feed_forward("routed_experts")
@@ -27,6 +40,8 @@ class RoutedExperts:
             roles += [TensorRole(f"experts.{e}.up.weight", (spec.intermediate, spec.hidden), True, True),
                       TensorRole(f"experts.{e}.down.weight", (spec.hidden, spec.intermediate), True, True)]
         return roles
+
+    gives_rows = True          # forward(..., summed=False) hands out RoutedRows
 
     def __init__(self, spec: RoutedExpertsSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
         if spec.activation not in ops.EXPERT_ACTIVATIONS or spec.activation == "none":
@@ -41,8 +56,9 @@ class RoutedExperts:
         self.down = torch.stack([ctx.matrix(tensors[f"experts.{e}.down.weight"]) for e in range(spec.experts)]).contiguous()
         self.tensor_cores = ctx.gemm != "library"
 
-    def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
-        """h [T, hidden] in the compute type -> the sum of the chosen experts' results, float32 [T, hidden]."""
+    def forward(self, h: torch.Tensor, batch, summed: bool = True):
+        """h [T, hidden] in the compute type -> the sum of the chosen experts' results, float32 [T, hidden]; or, with
+        `summed` False, the results as `RoutedRows`, for a consumer that adds them up itself."""
         if not isinstance(h, torch.Tensor):
             h = h.tensor()
         s, dev, ct = self.spec, h.device, self.ctx.compute_dtype
@@ -58,6 +74,8 @@ class RoutedExperts:
         ops.gemm_grouped(xp, self.up, offsets, hp, s.activation, self.ctx.status, self.tensor_cores)
         yp = torch.empty((A, s.hidden), dtype=torch.float32, device=dev)
         ops.gemm_grouped(hp, self.down, offsets, yp, "none", self.ctx.status, self.tensor_cores)
+        if not summed:
+            return RoutedRows(yp, row_of, weights.view(-1), s.top, not s.scale_input)
         out = torch.empty((T, s.hidden), dtype=torch.float32, device=dev)
         ops.route_combine(yp, weights.view(-1), row_of, out, s.top, scale=not s.scale_input)
         return out

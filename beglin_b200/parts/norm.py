@@ -40,7 +40,10 @@ class RMSNorm:
         lowp = None
         if want_lowp and self.ctx.compute_dtype != torch.float32:
             lowp = torch.empty(x.shape, dtype=self.ctx.compute_dtype, device=x.device)
-        ops.rmsnorm_add(x, y, self.weight, self.spec.eps, lowp)
+        if hasattr(y, "row_of"):               # the results of routed experts, not yet added up per token
+            ops.rmsnorm_add_routed(x, y.rows, y.row_of, y.weights, y.top, y.scale, self.weight, self.spec.eps, lowp)
+        else:
+            ops.rmsnorm_add(x, y, self.weight, self.spec.eps, lowp)
         return lowp
 
     def fusion(self):

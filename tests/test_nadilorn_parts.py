@@ -44,6 +44,26 @@ def test_rmsnorm_add(T, d, parts, ydt, lowp):
         assert torch.equal(lp, xd.to(torch.bfloat16))
 
 
+@pytest.mark.parametrize("T,d,top,scale,lowp", [(13, 24, 3, False, False), (70, 128, 2, True, True), (5, 37, 1, False, True)])
+def test_rmsnorm_add_of_routed_rows(T, d, top, scale, lowp):
+    """The norm on the result when the result is still the experts' rows: they are added up per token in rank order,
+    normed and added to the stream in one kernel."""
+    g = torch.Generator().manual_seed(T + d)
+    x = torch.randn(T, d, generator=g)
+    yp = torch.randn(T * top, d, generator=g) * 2
+    wts = torch.rand(T * top, generator=g)
+    row_of = torch.randperm(T * top, generator=g).int()
+    w = 1 + 0.3 * torch.randn(d, generator=g)
+    terms = yp.double()[row_of.long()] * (wts.double()[:, None] if scale else 1.0)
+    want = x.double() + plain.rms_norm(terms.reshape(T, top, d).sum(1), w.double(), 1e-5)
+    xd = x.to(DEV)
+    lp = torch.empty(T, d, dtype=torch.bfloat16, device=DEV) if lowp else None
+    ops().rmsnorm_add_routed(xd, yp.to(DEV), row_of.to(DEV), wts.to(DEV), top, scale, w.to(DEV), 1e-5, lp)
+    close(xd, want, 2e-6)
+    if lowp:
+        assert torch.equal(lp, xd.to(torch.bfloat16))
+
+
 # ----------------------------------------------------------------------------- query/key norm, rotation, append
 def scattered_tables(lengths, page, n_pages, seed):
     """A block table per request over pages handed out in a shuffled order."""
