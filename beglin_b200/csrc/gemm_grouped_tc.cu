@@ -188,6 +188,12 @@ extern "C" int bg_gemm_grouped_tc(const void* W, int E, int n_out, int K, int ld
         case 32: return grouped_launch<32, 4>(mw, mx, p, rows, stream);
         case 64: return grouped_launch<64, 4>(mw, mx, p, rows, stream);
         case 128: return grouped_launch<128, 3>(mw, mx, p, rows, stream);
-        default: return grouped_launch<256, 4>(mw, mx, p, rows, stream);
+        default: {
+            // many rows: bound by the tensor cores.  With more CTAs than SMs, two stages keep a CTA under half of an SM's
+            // shared memory, so that two CTAs share the SM and one's epilogue runs under the other's MMAs.
+            const long long ctas = (long long)((n_out + TC_BM - 1) / TC_BM) * (rows / 256 + E);
+            if (ctas > sm_count()) return grouped_launch<256, 2>(mw, mx, p, rows, stream);
+            return grouped_launch<256, 4>(mw, mx, p, rows, stream);
+        }
     }
 }

@@ -354,10 +354,11 @@ def test_route_sort(A, E):
 @pytest.mark.parametrize("E,N,K,loads,dtype,tc", [
     (5, 20, 72, [3, 0, 40, 1, 17], torch.float32, False), (3, 9, 33, [2, 2, 2], torch.float32, False),
     (8, 64, 128, [0, 100, 3, 0, 16, 17, 300, 1], torch.bfloat16, True), (4, 256, 64, [1, 0, 0, 2], torch.bfloat16, True),
-    (2, 130, 200, [700, 5], torch.bfloat16, True), (3, 40, 36, [9, 1, 50], torch.bfloat16, False), (1, 128, 64, [33], torch.bfloat16, True)])
+    (2, 130, 200, [700, 5], torch.bfloat16, True), (2, 1024, 64, [4000, 1100], torch.bfloat16, True), (3, 40, 36, [9, 1, 50], torch.bfloat16, False), (1, 128, 64, [33], torch.bfloat16, True)])
 @pytest.mark.parametrize("act", ["none", "relu2"])
 def test_grouped_product(E, N, K, loads, dtype, tc, act):
-    """Experts with unequal numbers of rows, some with none, on the CUDA-core kernel and on the tcgen05 kernel."""
+    """Experts with unequal numbers of rows, some with none, on the CUDA-core kernel and on the tcgen05 kernel (row tiles of
+    16 to 256; the last case has more CTAs than SMs, which run two to an SM with two stages each)."""
     o = ops()
     g = torch.Generator().manual_seed(E * N + K)
     A = sum(loads)
