@@ -114,31 +114,38 @@ route_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W, int
     if (warp < n) choose_experts(logit_s + warp * E, E, top, sigmoid, renorm, ids, weights, (size_t)(t0 + warp), lane);
 }
 
-// The same for a width that is a multiple of 8 and 16-byte aligned rows: warp w of a block takes token w, four experts at a
-// time; a lane walks the token's features in chunks of eight, 32 chunks apart (16-byte loads: one of the token's row, which
-// stays in the first-level cache from expert to expert, and two of each expert's row), and the warp adds up.  The walk
-// through the features one at a time above cost 53 us for 1,536 features whatever the number of tokens.
-template <typename TI>
+// The same for a width that is a multiple of 8 and 16-byte aligned rows.  A block of eight warps takes TPB tokens, 8 / TPB
+// warps to a token, which share the experts in groups of G; a lane walks the token's features in chunks of eight, 32 chunks
+// apart (16-byte loads: one of the token's row, which stays in the first-level cache from expert to expert, and two of
+// each expert's row), and the warp adds up; the first warp of a token then chooses.  Steps of many tokens: a warp per token,
+// four experts at a time.  Steps of few tokens: a block per token and an expert per warp at a time, so that a decoding step
+// spreads over as many SMs as it has tokens and a warp's chain of loads is one expert long.  (The walk through the features
+// one at a time above cost 53 us for 1,536 features whatever the number of tokens.)
+template <typename TI, int TPB, int G>
 __global__ void __launch_bounds__(32 * ROUTE_TOKENS)
 route_vec8_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W, int T, int d, int E, int top, int sigmoid,
                   int renorm, int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ logits_out) {
-    extern __shared__ float logit_s[];                     // [ROUTE_TOKENS][E]
+    constexpr int WPT = ROUTE_TOKENS / TPB;                // warps per token
+    extern __shared__ float logit_s[];                     // [TPB][E]
     pdl_launch();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * ROUTE_TOKENS + warp;
-    if (t >= T) return;                                    // (after the wait; the block's warps meet at no barrier)
-    const TI* row = h + (size_t)t * ldh;
-    float* sc = logit_s + warp * E;
+    const int tl = warp / WPT, wq = warp % WPT;
+    const int t = blockIdx.x * TPB + tl;
+    const bool live = t < T;
+    const TI* row = h + (size_t)(live ? t : 0) * ldh;
+    float* sc = logit_s + tl * E;
     const int d8 = d >> 3;
-    for (int e0 = 0; e0 < E; e0 += 4) {
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int e0 = wq * G; live && e0 < E; e0 += WPT * G) {
+        float acc[G];
+#pragma unroll
+        for (int u = 0; u < G; ++u) acc[u] = 0.0f;
 #pragma unroll 2
         for (int c = lane; c < d8; c += 32) {
             float hv[8];
             load8(row + 8 * c, hv);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < G; ++u) {
                 if (e0 + u < E) {
                     float wv[8];
                     load8(W + (size_t)(e0 + u) * d + 8 * c, wv);
@@ -148,7 +155,7 @@ route_vec8_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W
             }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < G; ++u) {
             const float v = warp_sum(acc[u]);
             if (lane == 0 && e0 + u < E) {
                 sc[e0 + u] = v;
@@ -156,8 +163,8 @@ route_vec8_kernel(const TI* __restrict__ h, int ldh, const float* __restrict__ W
             }
         }
     }
-    __syncwarp();
-    choose_experts(sc, E, top, sigmoid, renorm, ids, weights, (size_t)t, lane);
+    __syncthreads();                                       // every warp comes here, with or without a token
+    if (live && wq == 0) choose_experts(sc, E, top, sigmoid, renorm, ids, weights, (size_t)t, lane);
 }
 
 __global__ void __launch_bounds__(1024)
@@ -383,9 +390,12 @@ extern "C" int bg_route(const void* h, int h_dtype, int ldh, const float* W, int
     const size_t smem = (size_t)ROUTE_TOKENS * E * sizeof(float);
     if (smem > 40 * 1024) return BG_ERR_UNSUPPORTED;
     const dim3 grid((T + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(32 * ROUTE_TOKENS);
-    if (d % 8 == 0 && ldh % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)W % 16 == 0)
-        BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_vec8_kernel<TI>, grid, block, smem, stream, (const TI*)h, ldh, W, T, d, E, top,
-                                              sigmoid, renorm, ids, weights, logits_out));
+    if (d % 8 == 0 && ldh % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)W % 16 == 0 && T <= 256)
+        BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_vec8_kernel<TI, 1, 1>, dim3(T), block, (size_t)E * sizeof(float), stream,
+                                              (const TI*)h, ldh, W, T, d, E, top, sigmoid, renorm, ids, weights, logits_out));
+    else if (d % 8 == 0 && ldh % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)W % 16 == 0)
+        BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_vec8_kernel<TI, ROUTE_TOKENS, 4>, grid, block, smem, stream, (const TI*)h, ldh, W,
+                                              T, d, E, top, sigmoid, renorm, ids, weights, logits_out));
     else
         BG_DISPATCH_DTYPE(h_dtype, TI, launch(route_kernel<TI>, grid, block, smem, stream, (const TI*)h, ldh, W, T, d, E, top, sigmoid,
                                               renorm, ids, weights, logits_out));
