@@ -35,6 +35,9 @@ constexpr unsigned GP_OUT_BYTES = GP_BM * 128;                        // a stagi
 constexpr int GP_MODE_PLAIN = 0;           // out[t, n] (+ bias[n]) as bfloat16
 constexpr int GP_MODE_SWIGLU = 1;          // out[t, j] = silu(gate) * up, the weight's rows interleaved in blocks of 64
 constexpr int GP_MODE_RESIDUAL = 2;        // out (float, the residual stream) [t, n] += product (+ bias[n])
+constexpr int GP_MODE_GEGLU = 3;           // as GP_MODE_SWIGLU with the tanh form of GELU in silu's place
+// (a template instance of its own: the other modes' code is compiled as if it did not exist)
+__host__ __device__ constexpr bool gp_glu(int mode) { return mode == GP_MODE_SWIGLU || mode == GP_MODE_GEGLU; }
 // A tile is 256 tokens x BN output features, BN = 256, 192 or 128: a CTA loads BN / 2 rows of the weight.  The widest
 // tile that keeps the pairs of the device busy is chosen on the host: a narrow matrix has too few tiles of 256.
 template <int BN> struct GpTile {
@@ -225,7 +228,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 }
                 continue;
             }
-            constexpr int CHUNKS = MODE == GP_MODE_SWIGLU ? GP_BN / 128 : GP_BN / 64;
+            constexpr int CHUNKS = gp_glu(MODE) ? GP_BN / 128 : GP_BN / 64;
 #pragma unroll 1
             for (int c = 0; c < CHUNKS; ++c, ++q) {
                 unsigned char* buf = staging + (size_t)(q & 1) * GP_OUT_BYTES;
@@ -235,14 +238,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 for (int h = 0; h < 2; ++h) {
                     unsigned g[32], u[32];
                     float o[32];
-                    if (MODE == GP_MODE_SWIGLU) {
+                    if (gp_glu(MODE)) {
                         tc_ld32_nowait(t_addr + (unsigned)(c * 128 + h * 32), g);
                         tc_ld32_nowait(t_addr + (unsigned)(c * 128 + 64 + h * 32), u);
                         tc_wait_ld();
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
-                            o[j] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+                            if (MODE == GP_MODE_GEGLU)       // 0.5 g (1 + tanh(z)) = g sigmoid(2 z), z = sqrt(2/pi) (g + 0.044715 g^3)
+                                o[j] = __fdividef(gv, 1.0f + __expf(-1.5957691216057308f * (gv + 0.044715f * gv * gv * gv))) * uv;
+                            else
+                                o[j] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
                         }
                     } else {
                         tc_ld32_nowait(t_addr + (unsigned)(c * 64 + h * 32), g);
@@ -267,7 +273,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 asm volatile("bar.sync 1, 128;\n" ::: "memory");
                 if (elected) {
-                    const int col0 = MODE == GP_MODE_SWIGLU ? tn * (GP_BN / 2) + c * 64 : tn * GP_BN + c * 64;
+                    const int col0 = gp_glu(MODE) ? tn * (GP_BN / 2) + c * 64 : tn * GP_BN + c * 64;
                     tma_store_2d(&map_out, buf, col0, row0);
                     asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
                 }
@@ -327,14 +333,14 @@ static int gp_launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtenso
 // and 384 cycles per k-block for 256, 192 and 128 features.  Ties go to the wider tile.
 static int gp_tile_width(int T, int n_out, int mode) {
     static int forced = [] { const char* e = getenv("BEGLIN_B200_PAIR_BN"); return e ? atoi(e) : 0; }();
-    if (forced == 256 || forced == 128 || (forced == 192 && mode != GP_MODE_SWIGLU)) return forced;
+    if (forced == 256 || forced == 128 || (forced == 192 && !gp_glu(mode))) return forced;
     const int pairs = sm_count() / 2 > 0 ? sm_count() / 2 : 1;
     const int tiles_m = (T + 2 * GP_BM - 1) / (2 * GP_BM);
     const int widths[3] = {256, 192, 128}, cost[3] = {512, 448, 384};
     int best = 256;
     long long best_cost = -1;
     for (int i = 0; i < 3; ++i) {
-        if (widths[i] == 192 && mode == GP_MODE_SWIGLU) continue;         // gate and up come in blocks of 64 + 64
+        if (widths[i] == 192 && gp_glu(mode)) continue;                    // gate and up come in blocks of 64 + 64
         const long long tiles = (long long)tiles_m * ((n_out + widths[i] - 1) / widths[i]);
         const long long c = (tiles + pairs - 1) / pairs * cost[i];
         if (best_cost < 0 || c < best_cost) { best_cost = c; best = widths[i]; }
@@ -357,10 +363,10 @@ extern "C" int bg_gemm_pair(const void* W, int n_out, int K, int ldw, const void
                             void* out, int ldo, int mode, unsigned* status, cudaStream_t stream) {
     if (T <= 0 || n_out <= 0) return BG_OK;
     if (K <= 0) return BG_ERR_SHAPE;
-    if (mode != GP_MODE_PLAIN && mode != GP_MODE_SWIGLU && mode != GP_MODE_RESIDUAL) return BG_ERR_UNSUPPORTED;
+    if (mode != GP_MODE_PLAIN && mode != GP_MODE_SWIGLU && mode != GP_MODE_RESIDUAL && mode != GP_MODE_GEGLU) return BG_ERR_UNSUPPORTED;
     if ((ldw % 8) || (ldx % 8) || ((uintptr_t)W % 16) || ((uintptr_t)X % 16) || ((uintptr_t)out % 16)) return BG_ERR_ALIGN;
     if (mode == GP_MODE_RESIDUAL ? (ldo % 4) : (ldo % 8)) return BG_ERR_ALIGN;
-    if (mode == GP_MODE_SWIGLU && (n_out % 128 || bias)) return BG_ERR_SHAPE;
+    if (gp_glu(mode) && (n_out % 128 || bias)) return BG_ERR_SHAPE;
     const int bn = gp_tile_width(T, n_out, mode);
     PairParams p;
     p.bias = bias; p.n_out = n_out; p.T = T; p.K = K; p.status = status;
@@ -372,10 +378,12 @@ extern "C" int bg_gemm_pair(const void* W, int n_out, int K, int ldw, const void
     rc = make_map(&mx, X, T, K, ldx, GP_BM);
     if (rc != BG_OK) return rc;
     if (mode == GP_MODE_RESIDUAL) rc = make_map_f32(&mo, out, T, n_out, ldo, GP_BM);
-    else rc = make_map(&mo, out, T, mode == GP_MODE_SWIGLU ? n_out / 2 : n_out, ldo, GP_BM);
+    else rc = make_map(&mo, out, T, gp_glu(mode) ? n_out / 2 : n_out, ldo, GP_BM);
     if (rc != BG_OK) return rc;
     if (mode == GP_MODE_SWIGLU)
         return bn == 256 ? gp_launch<6, GP_MODE_SWIGLU, 256>(mx, mw, mo, p, stream) : gp_launch<8, GP_MODE_SWIGLU, 128>(mx, mw, mo, p, stream);
+    if (mode == GP_MODE_GEGLU)
+        return bn == 256 ? gp_launch<6, GP_MODE_GEGLU, 256>(mx, mw, mo, p, stream) : gp_launch<8, GP_MODE_GEGLU, 128>(mx, mw, mo, p, stream);
     if (mode == GP_MODE_PLAIN)
         return bn == 256 ? gp_launch<6, GP_MODE_PLAIN, 256>(mx, mw, mo, p, stream)
              : bn == 192 ? gp_launch<6, GP_MODE_PLAIN, 192>(mx, mw, mo, p, stream) : gp_launch<8, GP_MODE_PLAIN, 128>(mx, mw, mo, p, stream);

@@ -672,7 +672,8 @@ def gemm_bf16_tn_unchecked(x: torch.Tensor, w_ptr: int, n_out: int, k: int, ldw:
            "gemm_bf16_tn")
 
 
-PAIR_PLAIN, PAIR_SWIGLU, PAIR_RESIDUAL = 0, 1, 2
+PAIR_PLAIN, PAIR_SWIGLU, PAIR_RESIDUAL, PAIR_GEGLU = 0, 1, 2, 3       # PAIR_GEGLU: as PAIR_SWIGLU with the tanh form of GELU
+PAIR_GLU = {"silu": PAIR_SWIGLU, "gelu_tanh": PAIR_GEGLU}
 
 
 def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = PAIR_PLAIN,
@@ -684,7 +685,7 @@ def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = P
     _cuda(x, w, out, bias, status)
     N, K = w.shape
     T = x.shape[0]
-    cols = N // 2 if mode == PAIR_SWIGLU else N
+    cols = N // 2 if mode in (PAIR_SWIGLU, PAIR_GEGLU) else N
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or \
             out.dtype != (torch.float32 if mode == PAIR_RESIDUAL else torch.bfloat16):
         raise KernelError("gemm_pair takes bfloat16 operands and gives a bfloat16 result (adds to a float32 stream)")

@@ -75,13 +75,19 @@ class Linear:
         if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.shape[1] != self.in_features or x.stride(0) % 8:
             raise ops.KernelError(f"the fused product takes contiguous bfloat16 rows of {self.in_features} features")
 
-    def of(self, inp, swiglu: bool = False) -> torch.Tensor:
+    def pairs(self, T: int) -> bool:
+        """Whether a step of T rows runs the gated product of many rows on pairs of CTAs (and not the fused one of few)."""
+        return self._tc is not None and not self.fuses(T) and self._tc.pairs(T)
+
+    def of(self, inp, swiglu: bool = False, activation: str = "silu") -> torch.Tensor:
         """The product of `inp`, a tensor [T, in] or a NormedInput (a norm of the residual stream that has
         not been computed).  Where the fused product runs, the norm is applied to the operand inside it;
         the result is then complete ([T, out], float).  Else as `partial`.  With `swiglu` (the weight's
         rows interleaved in blocks of 64, gate then up) the result is silu(gate) * up, [T, out / 2] in the
         compute type (from the fused product of few rows or from the product of many rows on pairs of CTAs), or
-        None when this step runs neither."""
+        None when this step runs neither.  `activation` other than silu is known to the product of many rows only."""
+        if swiglu and activation != "silu" and not self.pairs(inp.rows if isinstance(inp, NormedInput) else inp.shape[0]):
+            return None
         lazy = isinstance(inp, NormedInput)
         T = inp.rows if lazy else inp.shape[0]
         if not self.fuses(T):
@@ -89,7 +95,7 @@ class Linear:
                 if self._tc is None or not self._tc.pairs(T):
                     return None
                 with ops.phase(self.label):
-                    return self._tc.pair_swiglu(inp.tensor() if lazy else inp)
+                    return self._tc.pair_swiglu(inp.tensor() if lazy else inp, activation)
             return self.partial(inp.tensor() if lazy else inp)
         fusion = inp.fusable() if lazy else None
         n = self.out_features // 2 if swiglu else self.out_features

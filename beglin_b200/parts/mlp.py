@@ -1,8 +1,8 @@
 """SwiGLU feed-forward: m = W_down (silu(W_gate h) * (W_up h)), no biases (qwen_infer.c:1560-1573,
 :727-733).  Gate and up run as one product over the concatenated matrix [2*im, d], as the
 reference fuses them (qwen_infer.c:1368-1402).  The spec's `activation` may name the tanh form of GELU in
-silu's place; the products with the activation in their epilogue know silu only, so that form runs the plain
-product and the activation kernel."""
+silu's place; of the products with the activation in their epilogue, the one of many rows (pairs of CTAs) knows both,
+the fused one of few rows silu only, so a decoding step with GELU runs the plain product and the activation kernel."""
 from __future__ import annotations
 
 from typing import Dict, List, Optional
@@ -31,7 +31,6 @@ class SwiGLU:
         if spec.activation not in ops.GLU_ACTIVATIONS:
             raise ValueError(f"unknown activation '{spec.activation}' of a gated feed-forward ({', '.join(ops.GLU_ACTIVATIONS)})")
         self.spec, self.ctx = spec, ctx
-        self.in_product = spec.activation == "silu"          # the fused epilogues compute silu
         gate, up, im = tensors["gate_proj.weight"], tensors["up_proj.weight"], spec.intermediate
         # Where the intermediate size allows it, the rows go in blocks of 64: gate, up, gate, up, ...  A CTA of
         # the fused product (128 rows) then holds 64 gate features with their 64 up features and applies
@@ -47,7 +46,7 @@ class SwiGLU:
     def forward(self, h, batch, stream: Optional[ResidualStream] = None) -> Optional[torch.Tensor]:
         """h: the normed rows, or a NormedInput.  With `stream` the result is added to it (or left owed to
         it) and None is returned; without, the addend is returned."""
-        act = self.gate_up.of(h, swiglu=True) if self.block and self.in_product else None
+        act = self.gate_up.of(h, swiglu=True, activation=self.spec.activation) if self.block else None
         if act is None:
             gu = self.gate_up.of(h)
             act = torch.empty((gu.shape[-2], self.spec.intermediate), dtype=self.ctx.compute_dtype, device=gu.device)

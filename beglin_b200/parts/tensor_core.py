@@ -107,12 +107,13 @@ class TensorCoreProduct:
         have too few 256 x 256 tiles for the pairs of the device."""
         return self.ctx.fuse and T >= PAIR_TOKENS and self.n_out % 128 == 0
 
-    def pair_swiglu(self, x: torch.Tensor) -> torch.Tensor:
-        """silu(gate) * up of x's rows, [T, n_out / 2] bfloat16; the weight's rows are interleaved in blocks of 64."""
+    def pair_swiglu(self, x: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+        """act(gate) * up of x's rows, [T, n_out / 2] bfloat16; the weight's rows are interleaved in blocks of 64; act is
+        silu or the tanh form of GELU."""
         if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.shape[1] != self.k or x.stride(0) % 8:
             raise ops.KernelError(f"the tcgen05 product takes contiguous bfloat16 rows of {self.k} features")
         out = torch.empty((x.shape[0], self.n_out // 2), dtype=torch.bfloat16, device=x.device)
-        ops.gemm_pair_unchecked(x, self._w_ptr, self.n_out, self.k, self._ldw, out, ops.PAIR_SWIGLU, self._status_ptr)
+        ops.gemm_pair_unchecked(x, self._w_ptr, self.n_out, self.k, self._ldw, out, ops.PAIR_GLU[activation], self._status_ptr)
         return out
 
     def pair_residual(self, x: torch.Tensor, bias: Optional[torch.Tensor], stream_x: torch.Tensor) -> None:

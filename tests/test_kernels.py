@@ -690,17 +690,19 @@ def test_gemm_pair_residual(ops, T, N, K, bias):
 @pytest.mark.gpu
 @pytest.mark.parametrize("T,im,K", [(256, 128, 64), (300, 320, 200), (2048, 8960 // 4, 1536), (999, 64, 136),
                                     (2048, 2048, 72)])
-def test_gemm_pair_swiglu(ops, T, im, K):
-    """The same with SwiGLU in the epilogue: the weight's rows are gate and up features interleaved in blocks of 64."""
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
+def test_gemm_pair_swiglu(ops, T, im, K, activation):
+    """The same with SwiGLU in the epilogue: the weight's rows are gate and up features interleaved in blocks of 64;
+    and with the tanh form of GELU in silu's place."""
     torch.manual_seed(T + im)
     x = (torch.randn(T, K) * 0.5).to(torch.bfloat16)
     gate = (torch.randn(im, K) * 0.08).to(torch.bfloat16)
     up = (torch.randn(im, K) * 0.08).to(torch.bfloat16)
     g, u = x.double() @ gate.double().t(), x.double() @ up.double().t()
-    want = g / (1.0 + torch.exp(-g)) * u
+    want = (g / (1.0 + torch.exp(-g)) if activation == "silu" else torch.nn.functional.gelu(g, approximate="tanh")) * u
     out = torch.full((T, im), float("nan"), dtype=torch.bfloat16, device=DEV)
     status = ops.new_status(DEV)
-    ops.gemm_pair(x.to(DEV), _interleave_gate_up(gate, up).contiguous().to(DEV), out, ops.PAIR_SWIGLU, None, status)
+    ops.gemm_pair(x.to(DEV), _interleave_gate_up(gate, up).contiguous().to(DEV), out, ops.PAIR_GLU[activation], None, status)
     ops.raise_on_status(status)
     assert torch.isfinite(out).all()
     assert (out.double().cpu() - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
